@@ -1,0 +1,120 @@
+/* limn_b200: fused scaled-dot-product attention for NVIDIA B200 (sm_100a), C ABI.
+ *
+ * These are the entry points a host binds in place of the three CUSTOM kernels limn's cuda
+ * device compiles with NVRTC (limn/backend_cuda.py:352-361 builds them from the emitters at
+ * limn/cuda_emit.py:921-1083). Every tensor is dense row-major with its leading dims
+ * flattened into `bh` independent problems, exactly as the reference's block decoding does
+ * (limn/cuda_emit.py:765-775, :853-862). All pointers are device pointers unless a function
+ * says otherwise; nothing here allocates per call, synchronises, or keeps a pointer after
+ * it returns. Kernels are enqueued on `stream` (NULL = the legacy default stream, which is
+ * where limn launches: limn/backend_cuda.py:413).
+ *
+ * Every function returns 0 on success and a non-zero code otherwise; the message for the
+ * calling thread's last failure is limn_b200_last_error(). The host binding turns that
+ * into the RuntimeError the reference raises from check() (limn/backend_cuda.py:154-162).
+ */
+#ifndef LIMN_B200_H
+#define LIMN_B200_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Storage dtypes of q, k, v, dO and the outputs (limn/ops.py:24-27). The row statistics
+ * L and delta are float32 for F32/F16/BF16 and float64 for F64 (limn/ops.py:53-62). */
+enum limn_b200_dtype {
+  LIMN_B200_F32 = 0,
+  LIMN_B200_F16 = 1,
+  LIMN_B200_BF16 = 2,
+  LIMN_B200_F64 = 3
+};
+
+enum limn_b200_status {
+  LIMN_B200_OK = 0,
+  LIMN_B200_BAD_ARGUMENT = 1,   /* null pointer, non-positive extent, causal with t_q != t_k, unknown dtype */
+  LIMN_B200_UNSUPPORTED = 2,    /* extents beyond what any kernel here serves */
+  LIMN_B200_CUDA_ERROR = 3,     /* a CUDA runtime/driver call failed; the message names it */
+  LIMN_B200_DEVICE_TIMEOUT = 4  /* a kernel gave up on a bounded wait; see limn_b200_device_status */
+};
+
+/* Which kernel family served (or would serve) a problem. */
+enum limn_b200_path {
+  LIMN_B200_PATH_GENERAL = 0,  /* SIMT kernels: any float dtype, any hd/hd_v, key mask, t_q != t_k */
+  LIMN_B200_PATH_TCGEN05 = 1   /* TMA + tcgen05 kernels: f16/bf16, hd == hd_v in {64, 128}, no key mask */
+};
+
+/* "sdpa": replaces emit_sdpa (limn/cuda_emit.py:921-965); oracle limn/sdpa.py:91-137.
+ *   q (bh, t_q, hd), k (bh, t_k, hd), v (bh, t_k, hd_v), key_mask (bh, t_k) in the same dtype
+ *   or NULL (0 hides a key), out (bh, t_q, hd_v) in the same dtype, lse (bh, t_q) float32
+ *   (float64 for F64). A query row with no visible key gets NaN and lse = -inf. */
+int limn_b200_sdpa_fwd(const void* q, const void* k, const void* v, const void* key_mask,
+                       void* out, void* lse,
+                       int dtype, long long bh, int t_q, int t_k, int hd, int hd_v,
+                       int causal, double scale, void* stream);
+
+/* "sdpa_bwd_q": replaces emit_sdpa_bwd_q (limn/cuda_emit.py:968-1005); oracle limn/sdpa.py:140-170.
+ *   dout (bh, t_q, hd_v); lse and delta (bh, t_q) in the statistics dtype; dq (bh, t_q, hd). */
+int limn_b200_sdpa_bwd_q(const void* q, const void* k, const void* v, const void* dout,
+                         const void* lse, const void* delta, const void* key_mask,
+                         void* dq,
+                         int dtype, long long bh, int t_q, int t_k, int hd, int hd_v,
+                         int causal, double scale, void* stream);
+
+/* "sdpa_bwd_kv": replaces emit_sdpa_bwd_kv (limn/cuda_emit.py:1008-1083); oracle limn/sdpa.py:173-203.
+ *   dk (bh, t_k, hd), dv (bh, t_k, hd_v). Rows of a hidden key are written as exact zeros. */
+int limn_b200_sdpa_bwd_kv(const void* q, const void* k, const void* v, const void* dout,
+                          const void* lse, const void* delta, const void* key_mask,
+                          void* dk, void* dv,
+                          int dtype, long long bh, int t_q, int t_k, int hd, int hd_v,
+                          int causal, double scale, void* stream);
+
+/* delta = sum_d dout * out per query row, in the statistics dtype: the row dot the frontend
+ * computes between the forward and the two backward ops (limn/tensor.py:705-706). Offered so
+ * a host that drives the three ops directly need not bring its own reduce kernel. */
+int limn_b200_sdpa_delta(const void* out, const void* dout, void* delta,
+                         int dtype, long long rows, int hd_v, void* stream);
+
+/* Which path the dispatcher picks for a problem (a limn_b200_path value), or -1 with an
+ * error message if the arguments are invalid. Launches nothing. */
+int limn_b200_sdpa_path(int dtype, long long bh, int t_q, int t_k, int hd, int hd_v,
+                        int causal, int has_mask, double scale);
+
+/* How many kernels the last successful limn_b200_sdpa_* call on this thread enqueued. */
+int limn_b200_last_launch_count(void);
+
+/* Message for the calling thread's most recent failure ("" if none). Stands where the
+ * driver's error string stands in limn/backend_cuda.py:154-162. */
+const char* limn_b200_last_error(void);
+
+/* Library version, major * 10000 + minor * 100 + patch. */
+int limn_b200_version(void);
+
+/* Kernels that wait (on TMA or tensor-core completion) give up after a bounded time and
+ * record a code in a per-device status word instead of hanging. This reads the word of the
+ * current device after synchronising it, and clears it; 0 means no kernel gave up. */
+int limn_b200_device_status(unsigned int* status);
+
+/* ---- plumbing for hosts without a CUDA binding of their own (tests, benchmark) ----
+ * limn itself allocates and copies through the driver API (limn/backend_cuda.py:297-326)
+ * and never calls these. */
+int limn_b200_device_count(int* count);
+int limn_b200_set_device(int ordinal);
+int limn_b200_mem_alloc(void** device_ptr, unsigned long long nbytes);
+int limn_b200_mem_free(void* device_ptr);
+int limn_b200_mem_set(void* device_ptr, int byte, unsigned long long nbytes, void* stream);
+int limn_b200_host_alloc(void** pinned_ptr, unsigned long long nbytes);
+int limn_b200_host_free(void* pinned_ptr);
+int limn_b200_copy_h2d(void* device_dst, const void* host_src, unsigned long long nbytes, void* stream);
+int limn_b200_copy_d2h(void* host_dst, const void* device_src, unsigned long long nbytes, void* stream);
+int limn_b200_copy_d2d(void* device_dst, const void* device_src, unsigned long long nbytes, void* stream);
+int limn_b200_stream_sync(void* stream);
+int limn_b200_device_sync(void);
+int limn_b200_event_create(void** event);
+int limn_b200_event_destroy(void* event);
+int limn_b200_event_record(void* event, void* stream);
+int limn_b200_event_elapsed_ms(void* start, void* stop, float* ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LIMN_B200_H */

@@ -1,0 +1,279 @@
+// The C ABI (include/limn_b200.h): argument checks, dispatch between the two kernel
+// families, error text, the per-device status word, and the small CUDA plumbing set that
+// hosts without their own binding use.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstring>
+#include <mutex>
+
+#include "common.h"
+#include "tensor_map.h"
+
+namespace limn_b200 {
+namespace {
+
+thread_local char g_error[512] = "";
+thread_local int g_launches = 0;
+
+constexpr int kMaxDevices = 64;
+std::mutex g_status_mutex;
+unsigned int* g_status_words[kMaxDevices] = {};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode_tiled = nullptr;
+std::once_flag g_encode_once;
+
+}  // namespace
+
+int fail(int code, const char* fmt, ...) {
+  va_list args;
+  va_start(args, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, args);
+  va_end(args);
+  return code;
+}
+
+void clear_error() { g_error[0] = '\0'; }
+void note_launches(int n) { g_launches += n; }
+
+int cuda_fail(cudaError_t err, const char* doing) {
+  return fail(LIMN_B200_CUDA_ERROR, "cuda: %s: %s", doing, cudaGetErrorString(err));
+}
+
+int status_word(unsigned int** word) {
+  int device = 0;
+  LIMN_CUDA(cudaGetDevice(&device), "asking for the current device");
+  if (device < 0 || device >= kMaxDevices) return fail(LIMN_B200_UNSUPPORTED, "device ordinal %d out of range", device);
+  std::lock_guard<std::mutex> lock(g_status_mutex);
+  if (g_status_words[device] == nullptr) {
+    unsigned int* fresh = nullptr;
+    LIMN_CUDA(cudaMalloc(&fresh, 256), "allocating the device status word");
+    LIMN_CUDA(cudaMemset(fresh, 0, 256), "clearing the device status word");
+    g_status_words[device] = fresh;
+  }
+  *word = g_status_words[device];
+  return LIMN_B200_OK;
+}
+
+int make_tile_map(CUtensorMap* map, const void* base, bool fp16, long long bh, int rows, int width, int box_rows) {
+  std::call_once(g_encode_once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult found;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &found) == cudaSuccess &&
+        found == cudaDriverEntryPointSuccess)
+      g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+  });
+  if (g_encode_tiled == nullptr)
+    return fail(LIMN_B200_CUDA_ERROR, "cuda: the driver does not export cuTensorMapEncodeTiled");
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0)
+    return fail(LIMN_B200_BAD_ARGUMENT, "sdpa: tensor base %p is not 16-byte aligned", base);
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(width), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(bh)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(width) * 2, static_cast<cuuint64_t>(rows) * width * 2};
+  const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  const CUresult res = g_encode_tiled(
+      map, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims,
+      strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (res != CUDA_SUCCESS) return fail(LIMN_B200_CUDA_ERROR, "cuda: encoding a tensor map failed with CUresult %d", (int)res);
+  return LIMN_B200_OK;
+}
+
+namespace {
+
+int check_problem(const char* name, const Problem& p) {
+  if (p.dtype < LIMN_B200_F32 || p.dtype > LIMN_B200_F64)
+    return fail(LIMN_B200_BAD_ARGUMENT, "%s: unknown dtype code %d", name, p.dtype);
+  if (p.bh < 0 || p.t_q <= 0 || p.t_k <= 0 || p.hd <= 0 || p.hd_v <= 0)
+    return fail(LIMN_B200_BAD_ARGUMENT, "%s: extents must be positive, got bh=%lld t_q=%d t_k=%d hd=%d hd_v=%d", name,
+                p.bh, p.t_q, p.t_k, p.hd, p.hd_v);
+  if (p.causal && p.t_q != p.t_k)
+    return fail(LIMN_B200_BAD_ARGUMENT, "%s: causal sdpa needs square keys, got %d queries and %d keys", name, p.t_q,
+                p.t_k);
+  return LIMN_B200_OK;
+}
+
+int run(Op op, const char* name, const Problem& p) {
+  clear_error();
+  g_launches = 0;
+  if (int rc = check_problem(name, p)) return rc;
+  const bool have_inputs = p.q && p.k && p.v;
+  bool have_rest = true;
+  switch (op) {
+    case Op::Fwd: have_rest = p.out && p.lse_out; break;
+    case Op::BwdQ: have_rest = p.dout && p.lse_in && p.delta && p.dq; break;
+    case Op::BwdKV: have_rest = p.dout && p.lse_in && p.delta && p.dk && p.dv; break;
+  }
+  if (!have_inputs || !have_rest) return fail(LIMN_B200_BAD_ARGUMENT, "%s: a required pointer is null", name);
+  if (p.bh == 0) return LIMN_B200_OK;
+  if (tcgen05_serves(op, p)) return tcgen05_launch(op, p);
+  return general_launch(op, p);
+}
+
+Problem problem(const void* q, const void* k, const void* v, const void* mask, int dtype, long long bh, int t_q,
+                int t_k, int hd, int hd_v, int causal, double scale, void* stream) {
+  Problem p;
+  p.q = q, p.k = k, p.v = v, p.mask = mask;
+  p.dtype = dtype, p.bh = bh, p.t_q = t_q, p.t_k = t_k, p.hd = hd, p.hd_v = hd_v;
+  p.causal = causal != 0, p.scale = scale, p.stream = static_cast<cudaStream_t>(stream);
+  return p;
+}
+
+}  // namespace
+}  // namespace limn_b200
+
+using namespace limn_b200;
+
+extern "C" {
+
+int limn_b200_sdpa_fwd(const void* q, const void* k, const void* v, const void* key_mask, void* out, void* lse,
+                       int dtype, long long bh, int t_q, int t_k, int hd, int hd_v, int causal, double scale,
+                       void* stream) {
+  Problem p = problem(q, k, v, key_mask, dtype, bh, t_q, t_k, hd, hd_v, causal, scale, stream);
+  p.out = out, p.lse_out = lse;
+  return run(Op::Fwd, "sdpa", p);
+}
+
+int limn_b200_sdpa_bwd_q(const void* q, const void* k, const void* v, const void* dout, const void* lse,
+                         const void* delta, const void* key_mask, void* dq, int dtype, long long bh, int t_q, int t_k,
+                         int hd, int hd_v, int causal, double scale, void* stream) {
+  Problem p = problem(q, k, v, key_mask, dtype, bh, t_q, t_k, hd, hd_v, causal, scale, stream);
+  p.dout = dout, p.lse_in = lse, p.delta = delta, p.dq = dq;
+  return run(Op::BwdQ, "sdpa_bwd_q", p);
+}
+
+int limn_b200_sdpa_bwd_kv(const void* q, const void* k, const void* v, const void* dout, const void* lse,
+                          const void* delta, const void* key_mask, void* dk, void* dv, int dtype, long long bh, int t_q,
+                          int t_k, int hd, int hd_v, int causal, double scale, void* stream) {
+  Problem p = problem(q, k, v, key_mask, dtype, bh, t_q, t_k, hd, hd_v, causal, scale, stream);
+  p.dout = dout, p.lse_in = lse, p.delta = delta, p.dk = dk, p.dv = dv;
+  return run(Op::BwdKV, "sdpa_bwd_kv", p);
+}
+
+int limn_b200_sdpa_delta(const void* out, const void* dout, void* delta, int dtype, long long rows, int hd_v,
+                         void* stream) {
+  clear_error();
+  g_launches = 0;
+  if (!out || !dout || !delta) return fail(LIMN_B200_BAD_ARGUMENT, "sdpa_delta: a required pointer is null");
+  if (rows < 0 || hd_v <= 0) return fail(LIMN_B200_BAD_ARGUMENT, "sdpa_delta: extents must be positive");
+  if (rows == 0) return LIMN_B200_OK;
+  return general_delta(out, dout, delta, dtype, rows, hd_v, static_cast<cudaStream_t>(stream));
+}
+
+int limn_b200_sdpa_path(int dtype, long long bh, int t_q, int t_k, int hd, int hd_v, int causal, int has_mask,
+                        double scale) {
+  clear_error();
+  static const int placeholder = 0;
+  Problem p = problem(&placeholder, &placeholder, &placeholder, has_mask ? &placeholder : nullptr, dtype, bh, t_q, t_k,
+                      hd, hd_v, causal, scale, nullptr);
+  if (check_problem("sdpa", p) != LIMN_B200_OK) return -1;
+  return tcgen05_serves(Op::Fwd, p) ? LIMN_B200_PATH_TCGEN05 : LIMN_B200_PATH_GENERAL;
+}
+
+int limn_b200_last_launch_count(void) { return g_launches; }
+const char* limn_b200_last_error(void) { return g_error; }
+int limn_b200_version(void) { return 100; }
+
+int limn_b200_device_status(unsigned int* status) {
+  clear_error();
+  if (!status) return fail(LIMN_B200_BAD_ARGUMENT, "device_status: null result pointer");
+  unsigned int* word = nullptr;
+  if (int rc = status_word(&word)) return rc;
+  LIMN_CUDA(cudaDeviceSynchronize(), "waiting for the device before reading its status word");
+  LIMN_CUDA(cudaMemcpy(status, word, sizeof(unsigned int), cudaMemcpyDeviceToHost), "reading the device status word");
+  if (*status != 0) LIMN_CUDA(cudaMemset(word, 0, sizeof(unsigned int)), "clearing the device status word");
+  return LIMN_B200_OK;
+}
+
+/* ---- plumbing ---- */
+int limn_b200_device_count(int* count) {
+  clear_error();
+  LIMN_CUDA(cudaGetDeviceCount(count), "counting devices");
+  return LIMN_B200_OK;
+}
+int limn_b200_set_device(int ordinal) {
+  clear_error();
+  LIMN_CUDA(cudaSetDevice(ordinal), "selecting a device");
+  return LIMN_B200_OK;
+}
+int limn_b200_mem_alloc(void** device_ptr, unsigned long long nbytes) {
+  clear_error();
+  LIMN_CUDA(cudaMalloc(device_ptr, nbytes ? nbytes : 1), "allocating device memory");
+  return LIMN_B200_OK;
+}
+int limn_b200_mem_free(void* device_ptr) {
+  clear_error();
+  LIMN_CUDA(cudaFree(device_ptr), "freeing device memory");
+  return LIMN_B200_OK;
+}
+int limn_b200_mem_set(void* device_ptr, int byte, unsigned long long nbytes, void* stream) {
+  clear_error();
+  LIMN_CUDA(cudaMemsetAsync(device_ptr, byte, nbytes, static_cast<cudaStream_t>(stream)), "filling device memory");
+  return LIMN_B200_OK;
+}
+int limn_b200_host_alloc(void** pinned_ptr, unsigned long long nbytes) {
+  clear_error();
+  LIMN_CUDA(cudaMallocHost(pinned_ptr, nbytes ? nbytes : 1), "allocating pinned host memory");
+  return LIMN_B200_OK;
+}
+int limn_b200_host_free(void* pinned_ptr) {
+  clear_error();
+  LIMN_CUDA(cudaFreeHost(pinned_ptr), "freeing pinned host memory");
+  return LIMN_B200_OK;
+}
+int limn_b200_copy_h2d(void* device_dst, const void* host_src, unsigned long long nbytes, void* stream) {
+  clear_error();
+  LIMN_CUDA(cudaMemcpyAsync(device_dst, host_src, nbytes, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)),
+            "uploading bytes");
+  return LIMN_B200_OK;
+}
+int limn_b200_copy_d2h(void* host_dst, const void* device_src, unsigned long long nbytes, void* stream) {
+  clear_error();
+  LIMN_CUDA(cudaMemcpyAsync(host_dst, device_src, nbytes, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)),
+            "downloading bytes");
+  return LIMN_B200_OK;
+}
+int limn_b200_copy_d2d(void* device_dst, const void* device_src, unsigned long long nbytes, void* stream) {
+  clear_error();
+  LIMN_CUDA(cudaMemcpyAsync(device_dst, device_src, nbytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)),
+            "copying bytes on the device");
+  return LIMN_B200_OK;
+}
+int limn_b200_stream_sync(void* stream) {
+  clear_error();
+  LIMN_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)), "waiting for a stream");
+  return LIMN_B200_OK;
+}
+int limn_b200_device_sync(void) {
+  clear_error();
+  LIMN_CUDA(cudaDeviceSynchronize(), "waiting for the device");
+  return LIMN_B200_OK;
+}
+int limn_b200_event_create(void** event) {
+  clear_error();
+  cudaEvent_t e;
+  LIMN_CUDA(cudaEventCreate(&e), "creating an event");
+  *event = e;
+  return LIMN_B200_OK;
+}
+int limn_b200_event_destroy(void* event) {
+  clear_error();
+  LIMN_CUDA(cudaEventDestroy(static_cast<cudaEvent_t>(event)), "destroying an event");
+  return LIMN_B200_OK;
+}
+int limn_b200_event_record(void* event, void* stream) {
+  clear_error();
+  LIMN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(event), static_cast<cudaStream_t>(stream)), "recording an event");
+  return LIMN_B200_OK;
+}
+int limn_b200_event_elapsed_ms(void* start, void* stop, float* ms) {
+  clear_error();
+  LIMN_CUDA(cudaEventElapsedTime(ms, static_cast<cudaEvent_t>(start), static_cast<cudaEvent_t>(stop)),
+            "reading an event interval");
+  return LIMN_B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,62 @@
+// Shared host-side declarations for the limn_b200 library: the problem description every
+// kernel family takes, error reporting, and the per-device status word.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/limn_b200.h"
+
+namespace limn_b200 {
+
+// One attention problem, as the C ABI received it. Pointers the op does not use are null.
+struct Problem {
+  const void* q = nullptr;
+  const void* k = nullptr;
+  const void* v = nullptr;
+  const void* dout = nullptr;
+  const void* lse_in = nullptr;  // backward: the forward's L
+  const void* delta = nullptr;   // backward: row dot of dO and O
+  const void* mask = nullptr;    // (bh, t_k) in the storage dtype, 0 hides a key; may be null
+  void* out = nullptr;           // forward: O
+  void* lse_out = nullptr;       // forward: L
+  void* dq = nullptr;
+  void* dk = nullptr;
+  void* dv = nullptr;
+  int dtype = 0;
+  long long bh = 0;
+  int t_q = 0, t_k = 0, hd = 0, hd_v = 0;
+  int causal = 0;
+  double scale = 0.0;
+  cudaStream_t stream = nullptr;
+};
+
+enum class Op { Fwd, BwdQ, BwdKV };
+
+// Error text for the calling thread; returns `code` so call sites can `return fail(...)`.
+int fail(int code, const char* fmt, ...);
+void clear_error();
+void note_launches(int n);
+
+// cudaError_t -> status code with a message naming what was being done.
+int cuda_fail(cudaError_t err, const char* doing);
+#define LIMN_CUDA(expr, doing)                                   \
+  do {                                                           \
+    cudaError_t err__ = (expr);                                  \
+    if (err__ != cudaSuccess) return ::limn_b200::cuda_fail(err__, doing); \
+  } while (0)
+
+// Device address of the current device's status word (allocated on first use, one per
+// device, zero-initialised). Kernels that wait write a non-zero code there when they give up.
+int status_word(unsigned int** word);
+
+// Kernel families. Each returns a status code and enqueues on p.stream.
+int general_launch(Op op, const Problem& p);
+int general_delta(const void* out, const void* dout, void* delta, int dtype, long long rows, int hd_v,
+                  cudaStream_t stream);
+bool tcgen05_serves(Op op, const Problem& p);
+int tcgen05_launch(Op op, const Problem& p);
+
+}  // namespace limn_b200

@@ -1,0 +1,26 @@
+// Which problems the TMA + tcgen05 kernels take, and the switch over the three ops.
+#include "common.h"
+
+namespace limn_b200 {
+
+int tcgen05_fwd(const Problem& p);
+
+bool tcgen05_serves(Op op, const Problem& p) {
+  if (op != Op::Fwd) return false;
+  if (p.dtype != LIMN_B200_BF16 && p.dtype != LIMN_B200_F16) return false;
+  if (p.hd != p.hd_v || (p.hd != 64 && p.hd != 128)) return false;
+  if (p.mask != nullptr) return false;
+  if (!(p.scale > 0.0)) return false;          // the softmax folds the scale into exp2 and takes row maxima before scaling
+  if (p.bh > 0x7fffffffLL) return false;       // problem index is a 32-bit TMA coordinate
+  return true;
+}
+
+int tcgen05_launch(Op op, const Problem& p) {
+  switch (op) {
+    case Op::Fwd: return tcgen05_fwd(p);
+    default: break;
+  }
+  return fail(LIMN_B200_UNSUPPORTED, "sdpa: no tcgen05 kernel for this op");
+}
+
+}  // namespace limn_b200

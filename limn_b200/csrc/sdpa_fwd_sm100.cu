@@ -1,0 +1,390 @@
+// "sdpa" forward for f16/bf16 with hd == hd_v in {64, 128}: TMA-staged tiles, tcgen05 MMAs
+// accumulating in tensor memory, online softmax with one thread per query row.
+//
+// One CTA owns two consecutive tiles of 128 query rows of one (batch, head) problem and
+// streams that problem's keys and values past them in tiles of 128 keys:
+//   S_t = Q_t K_j^T          tcgen05.mma, both operands K-major in shared memory, S_t in tensor memory
+//   P_t = exp2(S_t - m_t)    128 softmax threads per Q tile, one row each; P_t overwrites S_t as 16-bit
+//   O_t += P_t V_j           tcgen05.mma, A = P_t from tensor memory, B = V_j (MN-major) from shared memory
+// Two Q tiles per CTA keep the tensor pipe busy on one while the other is in its softmax.
+// Each output row has exactly one owner and is accumulated in a fixed key order, so two
+// runs give the same bits, as the kernel this replaces promises (limn/cuda_emit.py:748-752).
+//
+// Warp roles (10 warps): 0-3 softmax/epilogue of Q tile 0, 4-7 of Q tile 1, 8 TMA producer,
+// 9 MMA issuer and tensor-memory owner.
+//
+// Semantics follow the oracle (limn/sdpa.py:91-137): causal keeps key j for row i when
+// j <= i; O is rounded once from the fp32 accumulator; L = m + log(l) in natural log.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.h"
+#include "sm100_ptx.cuh"
+#include "tensor_map.h"
+
+namespace limn_b200 {
+namespace {
+
+using namespace ptx;
+
+constexpr int kTileRows = 128;   // query rows per Q tile, keys per K/V tile
+constexpr int kQTiles = 2;       // Q tiles per CTA
+constexpr int kThreads = 320;
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr uint32_t kTmemCols = 512;
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int D>
+struct FwdLayout {
+  static constexpr int kTileBytes = kTileRows * D * 2;
+  static constexpr int kAtomBytes = kTileRows * 128;        // one 64-element-wide column block of a tile
+  static constexpr int kStages = D == 128 ? 2 : 3;          // K and V rings, each this deep
+  static constexpr int kQOff = 0;
+  static constexpr int kKOff = kQOff + kQTiles * kTileBytes;
+  static constexpr int kVOff = kKOff + kStages * kTileBytes;
+  static constexpr int kBarOff = kVOff + kStages * kTileBytes;
+  static constexpr int kBytes = kBarOff + 256 + 1024;       // barriers + slack to align the base to 1024
+  // tensor-memory columns
+  static constexpr int kSCol = 0;                           // S_t at kSCol + 128 t (P_t overlays its first 64)
+  static constexpr int kOCol = 256;                         // O_t at kOCol + D t
+};
+
+// barrier indices inside the barrier block
+template <int D>
+struct FwdBars {
+  static constexpr int kS = FwdLayout<D>::kStages;
+  static constexpr int q_full = 0;               // + t
+  static constexpr int k_full = 2;               // + stage
+  static constexpr int k_empty = k_full + kS;
+  static constexpr int v_full = k_empty + kS;
+  static constexpr int v_empty = v_full + kS;
+  static constexpr int s_full = v_empty + kS;    // + t
+  static constexpr int p_full = s_full + 2;      // + t
+  static constexpr int o_full = p_full + 2;      // + t
+  static constexpr int count = o_full + 2;
+};
+
+struct FwdParams {
+  void* out;
+  float* lse;
+  unsigned* status;
+  int t_q, t_k;
+  int q_pairs;      // CTAs per problem
+  int kv_tiles;     // ceil(t_k / 128)
+  float scale;
+};
+
+template <int D, bool kCausal, bool kFp16>
+__global__ void __launch_bounds__(kThreads, 1)
+sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                const __grid_constant__ CUtensorMap map_v, const FwdParams prm) {
+  using L = FwdLayout<D>;
+  using B = FwdBars<D>;
+  extern __shared__ unsigned char smem_unaligned[];
+  __shared__ uint32_t tmem_slot;
+  __shared__ uint32_t abort_flag;
+
+  const uint32_t raw = smem_addr(smem_unaligned);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  const uint32_t bars = base + L::kBarOff;
+  auto bar = [&](int i) { return bars + 8u * i; };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ---- which rows this CTA owns ----
+  const int problem = blockIdx.x / prm.q_pairs;
+  const int pair = prm.q_pairs - 1 - (blockIdx.x - problem * prm.q_pairs);  // longest causal rows first
+  int n_kv[kQTiles];  // key tiles each Q tile consumes
+  int q0[kQTiles];
+#pragma unroll
+  for (int t = 0; t < kQTiles; ++t) {
+    q0[t] = (pair * kQTiles + t) * kTileRows;
+    int n = prm.kv_tiles;
+    if (kCausal) n = min(n, pair * kQTiles + t + 1);
+    n_kv[t] = q0[t] < prm.t_q ? n : 0;
+  }
+  const int n_max = max(n_kv[0], n_kv[1]);
+
+  // ---- set-up: barriers, tensor memory ----
+  if (threadIdx.x == 0) {
+    abort_flag = *reinterpret_cast<volatile unsigned*>(prm.status) != kStatusOk;
+    for (int i = 0; i < B::count; ++i) {
+      const bool softmax_arrives = i >= B::p_full && i < B::p_full + 2;
+      mbar_init(bar(i), softmax_arrives ? 128u : 1u);
+    }
+    mbar_init_fence();
+  }
+  __syncthreads();
+  if (abort_flag) return;  // an earlier kernel on this device gave up; do not pile on
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_addr(&tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+
+  bool ok = true;
+
+  if (warp == kProducerWarp) {
+    // ================= TMA producer =================
+    if (lane == 0) {
+      tma_prefetch_descriptor(&map_q);
+      tma_prefetch_descriptor(&map_k);
+      tma_prefetch_descriptor(&map_v);
+#pragma unroll
+      for (int t = 0; t < kQTiles; ++t) {
+        if (n_kv[t] == 0) continue;
+        mbar_expect_tx(bar(B::q_full + t), L::kTileBytes);
+#pragma unroll
+        for (int a = 0; a < D / 64; ++a)
+          tma_load_3d(base + L::kQOff + t * L::kTileBytes + a * L::kAtomBytes, &map_q, bar(B::q_full + t), a * 64, q0[t],
+                      problem);
+      }
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int stage = j % L::kStages;
+        const uint32_t wrap = (j / L::kStages) & 1;
+        ok = mbar_wait(bar(B::k_empty + stage), wrap ^ 1u, prm.status, 0x0100u | stage);
+        if (!ok) break;
+        mbar_expect_tx(bar(B::k_full + stage), L::kTileBytes);
+#pragma unroll
+        for (int a = 0; a < D / 64; ++a)
+          tma_load_3d(base + L::kKOff + stage * L::kTileBytes + a * L::kAtomBytes, &map_k, bar(B::k_full + stage), a * 64,
+                      j * kTileRows, problem);
+        ok = mbar_wait(bar(B::v_empty + stage), wrap ^ 1u, prm.status, 0x0110u | stage);
+        if (!ok) break;
+        mbar_expect_tx(bar(B::v_full + stage), L::kTileBytes);
+#pragma unroll
+        for (int a = 0; a < D / 64; ++a)
+          tma_load_3d(base + L::kVOff + stage * L::kTileBytes + a * L::kAtomBytes, &map_v, bar(B::v_full + stage), a * 64,
+                      j * kTileRows, problem);
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ================= MMA issuer =================
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = mma_idesc(kTileRows, kTileRows, kFp16, false, false);
+      constexpr uint32_t idesc_pv = mma_idesc(kTileRows, D, kFp16, false, true);
+      // S_t = Q_t K^T over the head dim, 16 elements per instruction
+      auto issue_s = [&](int t, int stage) {
+        const uint32_t q_tile = base + L::kQOff + t * L::kTileBytes;
+        const uint32_t k_tile = base + L::kKOff + stage * L::kTileBytes;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * L::kAtomBytes + (kk % 4) * 32;
+          mma_ss(tmem + L::kSCol + t * 128, smem_desc_sw128(q_tile + off, 0, 1024), smem_desc_sw128(k_tile + off, 0, 1024),
+                 idesc_s, kk > 0);
+        }
+      };
+      // O_t += P_t V over the 128 keys of the tile, 16 keys per instruction
+      auto issue_pv = [&](int t, int stage, bool first) {
+        const uint32_t v_tile = base + L::kVOff + stage * L::kTileBytes;
+#pragma unroll
+        for (int kk = 0; kk < kTileRows / 16; ++kk)
+          mma_ts(tmem + L::kOCol + t * D, tmem + L::kSCol + t * 128 + kk * 8,
+                 smem_desc_sw128(v_tile + kk * 16 * 128, L::kAtomBytes, 1024), idesc_pv, !(first && kk == 0));
+      };
+#pragma unroll
+      for (int t = 0; t < kQTiles; ++t)
+        if (n_kv[t] > 0 && ok) ok = mbar_wait(bar(B::q_full + t), 0, prm.status, 0x0200u | t);
+      if (ok && n_max > 0) {
+        ok = mbar_wait(bar(B::k_full + 0), 0, prm.status, 0x0210u);
+        if (ok) {
+          tc_fence_after_sync();
+#pragma unroll
+          for (int t = 0; t < kQTiles; ++t)
+            if (n_kv[t] > 0) {
+              issue_s(t, 0);
+              mma_commit(bar(B::s_full + t));
+            }
+          mma_commit(bar(B::k_empty + 0));
+        }
+      }
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int stage = j % L::kStages;
+        const uint32_t wrap = (j / L::kStages) & 1;
+        const int next = (j + 1) % L::kStages;
+        const uint32_t next_wrap = ((j + 1) / L::kStages) & 1;
+        ok = mbar_wait(bar(B::v_full + stage), wrap, prm.status, 0x0220u | stage);
+        bool issued_next = false;
+#pragma unroll
+        for (int t = 0; t < kQTiles; ++t) {
+          if (!ok || j >= n_kv[t]) continue;
+          ok = mbar_wait(bar(B::p_full + t), j & 1, prm.status, 0x0230u | t);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_pv(t, stage, j == 0);
+          if (j + 1 < n_kv[t]) {
+            ok = mbar_wait(bar(B::k_full + next), next_wrap, prm.status, 0x0240u | next);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_s(t, next);
+            mma_commit(bar(B::s_full + t));  // also covers the PV above: O_t is settled when S_t is ready
+            issued_next = true;
+          } else {
+            mma_commit(bar(B::o_full + t));
+          }
+        }
+        if (!ok) break;
+        mma_commit(bar(B::v_empty + stage));
+        if (issued_next) mma_commit(bar(B::k_empty + next));
+      }
+    }
+  } else {
+    // ================= softmax + epilogue, one thread per query row =================
+    const int t = warp >> 2;
+    const int row_in_tile = threadIdx.x & 127;
+    const int row = q0[t] + row_in_tile;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t t_s = tmem + lane_base + L::kSCol + t * 128;
+    const uint32_t t_o = tmem + lane_base + L::kOCol + t * D;
+    const float sl2 = prm.scale * kLog2e;
+    float m = -INFINITY, l = 0.f;
+    const int n = n_kv[t];
+    for (int j = 0; j < n; ++j) {
+      ok = mbar_wait(bar(B::s_full + t), j & 1, prm.status, 0x0300u | t);
+      if (!ok) break;
+      tc_fence_after_sync();
+      uint32_t s[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(t_s + 32 * c, s[c]);
+      tmem_ld_wait();
+      const int kv0 = j * kTileRows;
+      const bool diagonal = kCausal && kv0 + kTileRows > q0[t];     // some key of this tile is right of some row
+      const bool ragged = kv0 + kTileRows > prm.t_k;                // some key of this tile does not exist
+      if (diagonal || ragged) {
+        int limit = prm.t_k - kv0;                                  // keys [0, limit) of the tile are visible
+        if (kCausal) limit = min(limit, row - kv0 + 1);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i >= limit) s[c][i] = 0xff800000u;  // -inf
+      }
+      float mx = m;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[c][i]));
+      // mx is finite: key 0 of the first tile is visible to every row
+      const float alpha = exp2_approx((m - mx) * sl2);
+      const float shift = -mx * sl2;
+      float sum = 0.f;
+      uint32_t packed[2][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = exp2_approx(fmaf(__uint_as_float(s[c][i]), sl2, shift));
+          const float p1 = exp2_approx(fmaf(__uint_as_float(s[c][i + 1]), sl2, shift));
+          sum += p0 + p1;
+          packed[c >> 1][(c & 1) * 16 + (i >> 1)] = kFp16 ? pack_f16(p0, p1) : pack_bf16(p0, p1);
+        }
+      l = l * alpha + sum;
+      m = mx;
+      tmem_st32(t_s, packed[0]);
+      tmem_st32(t_s + 32, packed[1]);
+      // O_t was last written by the PV of tile j-1, which s_full also covers
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(t_o + 32 * c, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(t_o + 32 * c, o);
+        }
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      mbar_arrive(bar(B::p_full + t));
+    }
+    if (ok && n > 0) ok = mbar_wait(bar(B::o_full + t), 0, prm.status, 0x0310u | t);
+    if (ok && n > 0) {
+      tc_fence_after_sync();
+      const float inv = 1.f / l;
+      const long long out_row = static_cast<long long>(problem) * prm.t_q + row;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(t_o + 32 * c, o);
+        tmem_ld_wait();
+        if (row < prm.t_q) {
+          uint4* dst = reinterpret_cast<uint4*>(static_cast<unsigned char*>(prm.out) + (out_row * D + 32 * c) * 2);
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float a = __uint_as_float(o[v4 * 8 + 2 * i]) * inv;
+              const float b = __uint_as_float(o[v4 * 8 + 2 * i + 1]) * inv;
+              w[i] = kFp16 ? pack_f16(a, b) : pack_bf16(a, b);
+            }
+            dst[v4] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+      if (row < prm.t_q) prm.lse[out_row] = m * prm.scale + logf(l);
+    }
+  }
+
+  // ---- teardown ----
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    if (*reinterpret_cast<volatile unsigned*>(prm.status) != kStatusOk) {
+      // a wait gave up somewhere: give copies and MMAs still in flight time to land before the
+      // tensor memory and shared memory they target are released
+      for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    tc_fence_after_sync();
+    tmem_free(tmem, kTmemCols);
+  }
+}
+
+template <int D, bool kCausal, bool kFp16>
+int launch_fwd(const Problem& p) {
+  using L = FwdLayout<D>;
+  CUtensorMap map_q, map_k, map_v;
+  if (int rc = make_tile_map(&map_q, p.q, kFp16, p.bh, p.t_q, D, kTileRows)) return rc;
+  if (int rc = make_tile_map(&map_k, p.k, kFp16, p.bh, p.t_k, D, kTileRows)) return rc;
+  if (int rc = make_tile_map(&map_v, p.v, kFp16, p.bh, p.t_k, D, kTileRows)) return rc;
+  FwdParams prm;
+  prm.out = p.out;
+  prm.lse = static_cast<float*>(p.lse_out);
+  if (int rc = status_word(&prm.status)) return rc;
+  prm.t_q = p.t_q, prm.t_k = p.t_k;
+  prm.q_pairs = (p.t_q + kQTiles * kTileRows - 1) / (kQTiles * kTileRows);
+  prm.kv_tiles = (p.t_k + kTileRows - 1) / kTileRows;
+  prm.scale = static_cast<float>(p.scale);
+  const long long ctas = p.bh * prm.q_pairs;
+  if (ctas > 0x7fffffffLL) return fail(LIMN_B200_UNSUPPORTED, "sdpa: %lld CTAs exceed one grid", ctas);
+  auto kernel = sdpa_fwd_kernel<D, kCausal, kFp16>;
+  static bool sized = false;  // per instantiation
+  if (!sized) {
+    LIMN_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes),
+              "sizing shared memory for the sdpa kernel");
+    sized = true;
+  }
+  kernel<<<dim3(static_cast<unsigned>(ctas)), dim3(kThreads), L::kBytes, p.stream>>>(map_q, map_k, map_v, prm);
+  LIMN_CUDA(cudaGetLastError(), "launching the sdpa kernel");
+  note_launches(1);
+  return LIMN_B200_OK;
+}
+
+template <int D>
+int launch_fwd_d(const Problem& p) {
+  const bool fp16 = p.dtype == LIMN_B200_F16;
+  if (p.causal) return fp16 ? launch_fwd<D, true, true>(p) : launch_fwd<D, true, false>(p);
+  return fp16 ? launch_fwd<D, false, true>(p) : launch_fwd<D, false, false>(p);
+}
+
+}  // namespace
+
+int tcgen05_fwd(const Problem& p) { return p.hd == 128 ? launch_fwd_d<128>(p) : launch_fwd_d<64>(p); }
+
+}  // namespace limn_b200

@@ -1,0 +1,141 @@
+"""The drop-in point: builders for limn's CUSTOM registry on a cuda device.
+
+limn's plan executor asks `device.custom[name](node)` for a `Runner` once per plan and then
+calls `runner(inputs, outs)` every step (limn/jit.py:41, :109, :130-135, :213-224). The
+reference's CudaDevice fills the registry with a builder that emits CUDA C and compiles it
+with NVRTC (limn/backend_cuda.py:292-293, :352-361). `install(dev)` overwrites the three
+entries with builders that bind the prebuilt sm_100a kernels instead; nothing else in limn
+changes, and tensor.py's `has_custom` checks (limn/tensor.py:559, :696) keep passing.
+
+A builder reads only what the node states: `node.arg.name`, `node.arg.params == (causal,
+scale)`, `node.arg.outs`, and each `node.srcs[i].shape` / `.dtype.name`; so it works on
+limn's Node or on limn_b200.host's stand-ins alike. A Runner reads `.ptr` off every buffer
+on every call and keeps none of them, because a captured plan is replayed against new
+buffers each time (limn/capture.py:152-168). It launches on the legacy default stream, where
+limn's own kernels run (limn/backend_cuda.py:413), and does not synchronise: the device's
+finish() does that once per batch (limn/jit.py:183).
+"""
+
+from __future__ import annotations
+
+import math
+from collections.abc import Callable
+from typing import Any
+
+from limn_b200._lib import DTYPE_CODES, check, lib
+
+SDPA, SDPA_BWD_Q, SDPA_BWD_KV = "sdpa", "sdpa_bwd_q", "sdpa_bwd_kv"  # limn/sdpa.py:43-45
+NAMES = (SDPA, SDPA_BWD_Q, SDPA_BWD_KV)
+
+Runner = Callable[[list[Any], list[Any]], None]
+
+
+class Form:
+    """A CUSTOM attention node read as extents: what limn/cuda_emit.py:890-918 reads off the
+    same node. `inputs` is the op's input count without a key mask; one more means the last
+    one is the mask."""
+
+    def __init__(self, node: Any, inputs: int):
+        causal, scale = node.arg.params
+        q, k, v = node.srcs[:3]
+        if q.dtype.name not in DTYPE_CODES:
+            raise NotImplementedError(f"limn_b200: {node.arg.name} has no kernel for dtype {q.dtype.name}")
+        for src in (k, v):
+            if src.dtype.name != q.dtype.name:
+                raise ValueError(f"limn_b200: {node.arg.name} wants one dtype, got {q.dtype.name} and {src.dtype.name}")
+        if len(q.shape) < 2 or len(k.shape) != len(q.shape) or len(v.shape) != len(q.shape):
+            raise ValueError(f"limn_b200: {node.arg.name} wants 2D+ inputs of equal rank, got {q.shape}, {k.shape}, {v.shape}")
+        if q.shape[:-2] != k.shape[:-2] or q.shape[:-2] != v.shape[:-2] or k.shape[-2] != v.shape[-2]:
+            raise ValueError(f"limn_b200: {node.arg.name} shape mismatch: {q.shape}, {k.shape}, {v.shape}")
+        if q.shape[-1] != k.shape[-1]:
+            raise ValueError(f"limn_b200: {node.arg.name}: head dims differ, {q.shape[-1]} and {k.shape[-1]}")
+        if causal and q.shape[-2] != k.shape[-2]:
+            raise ValueError(
+                f"limn_b200: causal {node.arg.name} needs square keys, got {q.shape[-2]} queries and {k.shape[-2]} keys"
+            )
+        if len(node.srcs) not in (inputs, inputs + 1):
+            raise ValueError(f"limn_b200: {node.arg.name} takes {inputs} inputs and an optional key mask, got {len(node.srcs)}")
+        self.name = node.arg.name
+        self.causal = bool(causal)
+        self.scale = float(scale)
+        self.dtype = DTYPE_CODES[q.dtype.name]
+        self.bh = math.prod(q.shape[:-2])
+        self.t_q, self.t_k = q.shape[-2], k.shape[-2]
+        self.hd, self.hd_v = q.shape[-1], v.shape[-1]
+        self.has_mask = len(node.srcs) > inputs
+        self.inputs = len(node.srcs)
+        self.outputs = len(node.arg.outs)
+
+    def tail(self) -> tuple:
+        return (self.dtype, self.bh, self.t_q, self.t_k, self.hd, self.hd_v, int(self.causal), self.scale, None)
+
+
+def _pointers(form: Form, inputs: list[Any], outs: list[Any]) -> tuple[list[int], list[int]]:
+    if len(inputs) != form.inputs or len(outs) != form.outputs:
+        raise RuntimeError(
+            f"limn_b200: {form.name} was built for {form.inputs} inputs and {form.outputs} outputs, "
+            f"called with {len(inputs)} and {len(outs)}"
+        )
+    return [buf.ptr for buf in inputs], [buf.ptr for buf in outs]
+
+
+def build_sdpa(node: Any) -> Runner:
+    """Runner for "sdpa": inputs (q, k, v[, mask]) -> outs (O, L). Stands where
+    CudaDevice._sdpa_runner stands for this name (limn/backend_cuda.py:352-361)."""
+    form = Form(node, 3)
+    fn = lib().limn_b200_sdpa_fwd
+    tail = form.tail()
+
+    def run(inputs: list[Any], outs: list[Any]) -> None:
+        ins, (out, lse) = _pointers(form, inputs, outs)
+        mask = ins[3] if form.has_mask else None
+        check(fn(ins[0], ins[1], ins[2], mask, out, lse, *tail), "launching sdpa")
+
+    return run
+
+
+def build_sdpa_bwd_q(node: Any) -> Runner:
+    """Runner for "sdpa_bwd_q": inputs (q, k, v, dO, L, delta[, mask]) -> outs (dQ,)."""
+    form = Form(node, 6)
+    fn = lib().limn_b200_sdpa_bwd_q
+    tail = form.tail()
+
+    def run(inputs: list[Any], outs: list[Any]) -> None:
+        ins, (dq,) = _pointers(form, inputs, outs)
+        mask = ins[6] if form.has_mask else None
+        check(fn(ins[0], ins[1], ins[2], ins[3], ins[4], ins[5], mask, dq, *tail), "launching sdpa_bwd_q")
+
+    return run
+
+
+def build_sdpa_bwd_kv(node: Any) -> Runner:
+    """Runner for "sdpa_bwd_kv": inputs (q, k, v, dO, L, delta[, mask]) -> outs (dK, dV)."""
+    form = Form(node, 6)
+    fn = lib().limn_b200_sdpa_bwd_kv
+    tail = form.tail()
+
+    def run(inputs: list[Any], outs: list[Any]) -> None:
+        ins, (dk, dv) = _pointers(form, inputs, outs)
+        mask = ins[6] if form.has_mask else None
+        check(fn(ins[0], ins[1], ins[2], ins[3], ins[4], ins[5], mask, dk, dv, *tail), "launching sdpa_bwd_kv")
+
+    return run
+
+
+BUILDERS: dict[str, Callable[[Any], Runner]] = {
+    SDPA: build_sdpa,
+    SDPA_BWD_Q: build_sdpa_bwd_q,
+    SDPA_BWD_KV: build_sdpa_bwd_kv,
+}
+
+
+def install(device: Any) -> Any:
+    """Register the three builders on a device that has a `custom` registry (limn's
+    CompiledDevice, limn/jit.py:103-135). Loads the shared library first, so a missing or
+    unloadable library fails here rather than at the first step."""
+    lib()
+    if not hasattr(device, "custom"):
+        raise TypeError(f"limn_b200.install: {type(device).__name__} has no CUSTOM registry")
+    for name, build in BUILDERS.items():
+        device.custom[name] = build
+    return device

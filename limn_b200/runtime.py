@@ -1,0 +1,102 @@
+"""Device memory for hosts that do not bring their own CUDA binding (the tests, the benchmark).
+
+limn's cuda device allocates through the driver API and hands the kernels `CudaBuffer`
+objects carrying `.ptr` and `.nbytes` (limn/backend_cuda.py:230-244). `DeviceBuffer` is the
+same shape of object over the library's own plumbing calls, so a Runner built by
+limn_b200.registry runs unchanged on either.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+
+from limn_b200._lib import check, lib
+
+
+class DeviceBuffer:
+    """nbytes of device memory; freed when the last reference drops."""
+
+    __slots__ = ("ptr", "nbytes")
+
+    def __init__(self, nbytes: int):
+        ptr = ctypes.c_void_p()
+        check(lib().limn_b200_mem_alloc(ctypes.byref(ptr), nbytes), f"allocating {nbytes} bytes")
+        self.ptr = ptr.value or 0
+        self.nbytes = nbytes
+
+    def __del__(self) -> None:
+        try:
+            if self.ptr:
+                lib().limn_b200_mem_free(self.ptr)
+                self.ptr = 0
+        except Exception:  # interpreter teardown
+            pass
+
+
+def set_device(ordinal: int) -> None:
+    check(lib().limn_b200_set_device(ordinal), f"selecting device {ordinal}")
+
+
+def device_count() -> int:
+    count = ctypes.c_int()
+    check(lib().limn_b200_device_count(ctypes.byref(count)), "counting devices")
+    return count.value
+
+
+def upload(array: np.ndarray) -> DeviceBuffer:
+    data = np.ascontiguousarray(array)
+    buf = DeviceBuffer(data.nbytes)
+    check(lib().limn_b200_copy_h2d(buf.ptr, data.ctypes.data, data.nbytes, None), "uploading bytes")
+    check(lib().limn_b200_device_sync(), "waiting for an upload")
+    return buf
+
+
+def empty(nbytes: int, poison: int | None = 0xFF) -> DeviceBuffer:
+    """Uninitialised output memory, as limn hands a kernel (limn/jit.py:173); filled with a
+    poison byte so a kernel that leaves a gap shows it."""
+    buf = DeviceBuffer(nbytes)
+    if poison is not None and nbytes:
+        check(lib().limn_b200_mem_set(buf.ptr, poison, nbytes, None), "poisoning an output")
+    return buf
+
+
+def download(buf: DeviceBuffer, dtype, shape) -> np.ndarray:
+    check(lib().limn_b200_device_sync(), "waiting for the device")
+    out = np.empty(buf.nbytes, dtype=np.uint8)
+    check(lib().limn_b200_copy_d2h(out.ctypes.data, buf.ptr, buf.nbytes, None), "downloading bytes")
+    check(lib().limn_b200_device_sync(), "waiting for a download")
+    return out.view(dtype).reshape(shape)
+
+
+def synchronize() -> None:
+    check(lib().limn_b200_device_sync(), "waiting for the device")
+
+
+def device_status() -> int:
+    """The current device's kernel status word (0 = no kernel gave up on a wait); clears it."""
+    word = ctypes.c_uint()
+    check(lib().limn_b200_device_status(ctypes.byref(word)), "reading the device status word")
+    return word.value
+
+
+class Event:
+    def __init__(self) -> None:
+        handle = ctypes.c_void_p()
+        check(lib().limn_b200_event_create(ctypes.byref(handle)), "creating an event")
+        self.handle = handle.value
+
+    def record(self, stream=None) -> None:
+        check(lib().limn_b200_event_record(self.handle, stream), "recording an event")
+
+    def ms_since(self, start: "Event") -> float:
+        ms = ctypes.c_float()
+        check(lib().limn_b200_event_elapsed_ms(start.handle, self.handle, ctypes.byref(ms)), "reading an event interval")
+        return ms.value
+
+    def __del__(self) -> None:
+        try:
+            lib().limn_b200_event_destroy(self.handle)
+        except Exception:
+            pass

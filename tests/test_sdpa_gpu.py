@@ -1,0 +1,182 @@
+"""Parity of the CUDA kernels, called through the C ABI and the registry builders, against
+the reference-made golden vectors and the CPU oracle. Shaped after the reference's own
+cuda-vs-numpy tests (tests/test_attention.py:243-396 there)."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+from conftest import BF16, golden, widen
+
+from oracle import sdpa_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+
+# max-abs gates: 1e-4 for fp32 inputs, 2e-2 for bf16 inputs, 1e-3 for the log-sum-exp; fp16 and
+# fp64 take the reference's own cuda-vs-numpy tolerances (tests/test_attention.py:250-255, :303-308
+# and limn/sdpa.py:285).
+FWD_TOL = {"float32": 1e-4, "bfloat16": 2e-2, "float16": 2e-3, "float64": 1e-11}
+BWD_TOL = {"float32": 1e-4, "bfloat16": 2e-2, "float16": 4e-3, "float64": 1e-11}
+LSE_TOL = 1e-3
+
+
+@pytest.fixture(scope="module")
+def dev():
+    from limn_b200 import host
+
+    return host.Device()
+
+
+def max_abs(got, want) -> float:
+    return float(np.abs(widen(got).astype(np.float64) - widen(want).astype(np.float64)).max())
+
+
+def close(got, want, tol, what) -> None:
+    """max-abs <= tol where values are order 1; relative to the answer's size where they are
+    larger (the reference's own measure, limn/sdpa.py:251-259)."""
+    assert got.shape == want.shape and got.dtype == want.dtype, what
+    assert not np.isnan(widen(got)).any(), f"{what}: NaN in result"
+    err = oracle.worst(widen(got), widen(want))
+    assert err <= tol, f"{what}: error {err:.3e} > {tol:g} (max-abs {max_abs(got, want):.3e})"
+
+
+@pytest.mark.parametrize("name", golden().names())
+def test_kernels_match_reference_golden(name, dev, golden):
+    from limn_b200 import host
+
+    q, k, v, do, mask, causal, scale = golden.inputs(name)
+    dtype = golden.cases[name][1]
+    att = host.Attention(dev, q, k, v, causal=causal, key_mask=mask)
+    out, lse = att.forward()
+    close(out, golden.output(name, "out"), FWD_TOL[dtype], f"{name} O")
+    close(lse, golden.output(name, "lse"), LSE_TOL if dtype != "float64" else 1e-11, f"{name} L")
+    dq, dk, dv = att.backward(do)
+    for got, key in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
+        close(got, golden.output(name, key), BWD_TOL[dtype], f"{name} {key}")
+
+
+def _random_case(seed, dtype, qs, ks, vs, q_mul=1.0, v_uniform=False):
+    rng = np.random.default_rng(seed)
+    q = (rng.standard_normal(qs) * q_mul).astype(dtype)
+    k = (rng.standard_normal(ks) * q_mul).astype(dtype)
+    v = (rng.uniform(-1, 1, vs) if v_uniform else rng.standard_normal(vs)).astype(dtype)
+    do = rng.standard_normal(qs[:-1] + vs[-1:]).astype(dtype)
+    return q, k, v, do
+
+
+ORACLE_CASES = [
+    # id, dtype, q, k, v shapes, causal, q/k multiplier, uniform V
+    ("bf16 d128 causal 5 tiles", BF16, (2, 3, 640, 128), (2, 3, 640, 128), (2, 3, 640, 128), True, 0.5, False),
+    ("bf16 d128 causal ragged 1000 sharp", BF16, (1, 3, 1000, 128), (1, 3, 1000, 128), (1, 3, 1000, 128), True, 2.0, True),
+    ("bf16 d64 full 2048", BF16, (1, 2, 2048, 64), (1, 2, 2048, 64), (1, 2, 2048, 64), False, 1.0, False),
+    ("bf16 d64 causal 256 batch", BF16, (4, 8, 256, 64), (4, 8, 256, 64), (4, 8, 256, 64), True, 1.0, False),
+    ("bf16 d128 rect 129x257", BF16, (3, 129, 128), (3, 257, 128), (3, 257, 128), False, 1.0, False),
+    ("bf16 d64 one row", BF16, (2, 1, 64), (2, 300, 64), (2, 300, 64), False, 1.0, False),
+    ("f16 d64 causal 384", np.float16, (2, 384, 64), (2, 384, 64), (2, 384, 64), True, 1.0, False),
+    ("f16 d128 full 200", np.float16, (2, 200, 128), (2, 200, 128), (2, 200, 128), False, 1.0, False),
+    ("f32 d64 causal 300", np.float32, (2, 300, 64), (2, 300, 64), (2, 300, 64), True, 1.0, False),
+    ("f32 d128 full 130", np.float32, (130, 128), (130, 128), (130, 128), False, 1.0, False),
+    ("bf16 d32 causal (general path)", BF16, (2, 2, 200, 32), (2, 2, 200, 32), (2, 2, 200, 32), True, 1.0, False),
+    ("bf16 hd 64 hd_v 128 (general path)", BF16, (2, 150, 64), (2, 150, 64), (2, 150, 128), False, 1.0, False),
+    ("f64 d40", np.float64, (2, 70, 40), (2, 70, 40), (2, 70, 24), True, 1.0, False),
+]
+
+
+@pytest.mark.parametrize("case", ORACLE_CASES, ids=[c[0] for c in ORACLE_CASES])
+def test_kernels_match_oracle(case, dev):
+    from limn_b200 import host
+
+    _, dtype, qs, ks, vs, causal, mul, uniform = case
+    q, k, v, do = _random_case(100 + len(qs) + qs[-2], dtype, qs, ks, vs, mul, uniform)
+    name = np.dtype(dtype).name
+    att = host.Attention(dev, q, k, v, causal=causal)
+    out, lse = att.forward()
+    scale = qs[-1] ** -0.5
+    want_out, want_lse = oracle.sdpa_forward(q, k, v, causal=causal, scale=scale)
+    close(out, want_out, FWD_TOL[name], "O")
+    close(lse, want_lse, LSE_TOL if name != "float64" else 1e-11, "L")
+    # the backward kernels read the device's own O and L, as they do under autograd
+    dq, dk, dv = att.backward(do)
+    delta = oracle.row_delta(do, want_out)
+    want_dq = oracle.sdpa_backward_q(q, k, v, do, want_lse, delta, causal=causal, scale=scale)
+    want_dk, want_dv = oracle.sdpa_backward_kv(q, k, v, do, want_lse, delta, causal=causal, scale=scale)
+    for got, want, what in ((dq, want_dq, "dQ"), (dk, want_dk, "dK"), (dv, want_dv, "dV")):
+        close(got, want, BWD_TOL[name], what)
+
+
+@pytest.mark.parametrize("t", list(range(1, 12)) + [63, 64, 65, 127, 128, 129, 255, 256, 257, 383, 385])
+def test_every_tail_length_d64_bf16(t, dev):
+    """Sequence lengths around every tile edge, causal and full, through the tensor-core path."""
+    from limn_b200 import host
+
+    for causal in (True, False):
+        q, k, v, do = _random_case(t, BF16, (2, t, 64), (2, t, 64), (2, t, 64))
+        att = host.Attention(dev, q, k, v, causal=causal)
+        out, lse = att.forward()
+        want_out, want_lse = oracle.sdpa_forward(q, k, v, causal=causal, scale=0.125)
+        close(out, want_out, 2e-2, f"t={t} causal={causal} O")
+        close(lse, want_lse, LSE_TOL, f"t={t} causal={causal} L")
+        dq, dk, dv = att.backward(do)
+        delta = oracle.row_delta(do, want_out)
+        close(dq, oracle.sdpa_backward_q(q, k, v, do, want_lse, delta, causal=causal, scale=0.125), 2e-2, f"t={t} dQ")
+        want_dk, want_dv = oracle.sdpa_backward_kv(q, k, v, do, want_lse, delta, causal=causal, scale=0.125)
+        close(dk, want_dk, 2e-2, f"t={t} dK")
+        close(dv, want_dv, 2e-2, f"t={t} dV")
+
+
+def test_two_runs_give_the_same_bits(dev):
+    from limn_b200 import host
+
+    for dtype, shape in ((BF16, (2, 2, 300, 128)), (np.float32, (2, 3, 64, 16))):
+        q, k, v, do = _random_case(5, dtype, shape, shape, shape)
+        runs = []
+        for _ in range(2):
+            att = host.Attention(dev, q, k, v, causal=True)
+            out, lse = att.forward()
+            runs.append((out, lse, *att.backward(do)))
+        for first, second in zip(*runs, strict=True):
+            np.testing.assert_array_equal(first.view(np.uint8), second.view(np.uint8))
+
+
+def test_hidden_keys_get_exactly_zero_gradients(dev):
+    from limn_b200 import host
+
+    q, k, v, do = _random_case(9, np.float32, (2, 3, 32, 8), (2, 3, 32, 8), (2, 3, 32, 12))
+    mask = np.broadcast_to(np.arange(32) < 20, (2, 3, 32)).astype(np.float32)
+    att = host.Attention(dev, q, k, v, causal=True, key_mask=mask)
+    att.forward()
+    _, dk, dv = att.backward(do)
+    assert (dk[..., 20:, :] == 0).all() and (dv[..., 20:, :] == 0).all()
+    assert np.abs(dk[..., :20, :]).min() > 0
+
+
+def test_row_without_a_visible_key_is_nan_with_minus_inf_lse(dev):
+    from limn_b200 import host
+
+    q, k, v, _ = _random_case(10, np.float32, (2, 8, 4), (2, 8, 4), (2, 8, 4))
+    mask = np.ones((2, 8), np.float32)
+    mask[1] = 0
+    out, lse = host.Attention(dev, q, k, v, key_mask=mask).forward()
+    assert np.isfinite(out[0]).all() and np.isnan(out[1]).all()
+    assert np.isneginf(lse[1]).all()
+
+
+def test_tensor_core_path_is_the_one_that_serves_the_tuned_shapes():
+    from limn_b200._lib import PATH_GENERAL, PATH_TCGEN05, lib
+
+    path = lib().limn_b200_sdpa_path
+    assert path(2, 256, 4096, 4096, 128, 128, 1, 0, 128**-0.5) == PATH_TCGEN05
+    assert path(2, 256, 256, 256, 64, 64, 1, 0, 0.125) == PATH_TCGEN05
+    assert path(1, 4, 100, 300, 64, 64, 0, 0, 0.125) == PATH_TCGEN05
+    assert path(0, 2, 128, 128, 32, 32, 1, 0, 32**-0.5) == PATH_GENERAL
+    assert path(2, 2, 128, 128, 64, 64, 0, 1, 0.125) == PATH_GENERAL
+
+
+def test_launch_errors_surface_as_runtime_errors(dev):
+    from limn_b200 import host
+
+    with pytest.raises(ValueError, match="square keys"):
+        host.Attention(dev, np.zeros((4, 8), np.float32), np.zeros((5, 8), np.float32), np.zeros((5, 8), np.float32), causal=True)
+    lib = __import__("limn_b200._lib", fromlist=["lib"]).lib()
+    assert lib.limn_b200_sdpa_fwd(None, None, None, None, None, None, 0, 1, 4, 4, 8, 8, 0, 1.0, None) == 1
+    assert b"null" in lib.limn_b200_last_error()
