@@ -1,0 +1,182 @@
+"""The drop-in boundary without a GPU: the library loads and exports every symbol the header
+declares, argument checks answer before any CUDA call, and the registry builders read nodes
+the way limn's own cuda device does."""
+
+from __future__ import annotations
+
+import re
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+REFERENCE = Path("/root/reference")
+
+
+def declared_functions() -> list[str]:
+    text = (ROOT / "include" / "limn_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return re.findall(r"\b(limn_b200_[a-z0-9_]+)\s*\(", text)
+
+
+def test_library_exports_every_declared_symbol():
+    from limn_b200._lib import SIGNATURES, lib
+
+    names = declared_functions()
+    assert len(names) >= 25 and len(set(names)) == len(names)
+    loaded = lib()
+    for name in names:
+        assert hasattr(loaded, name), f"{name} is declared in include/limn_b200.h but not exported"
+    assert set(names) == set(SIGNATURES), "the ctypes table and the header disagree"
+    assert loaded.limn_b200_version() >= 100
+
+
+def test_argument_checks_answer_without_a_device():
+    from limn_b200._lib import lib
+
+    fwd = lib().limn_b200_sdpa_fwd
+    err = lambda: lib().limn_b200_last_error().decode()
+    one = 1  # any non-null pointer value; the checks below fail before anything is dereferenced
+    assert fwd(one, one, one, None, one, one, 9, 1, 4, 4, 8, 8, 0, 1.0, None) == 1 and "dtype" in err()
+    assert fwd(one, one, one, None, one, one, 0, 1, 4, 5, 8, 8, 1, 1.0, None) == 1 and "square keys" in err()
+    assert fwd(one, one, one, None, one, one, 0, 1, 0, 4, 8, 8, 0, 1.0, None) == 1 and "positive" in err()
+    assert fwd(None, one, one, None, one, one, 0, 1, 4, 4, 8, 8, 0, 1.0, None) == 1 and "null" in err()
+    assert lib().limn_b200_sdpa_bwd_q(one, one, one, one, one, None, None, one, 0, 1, 4, 4, 8, 8, 0, 1.0, None) == 1
+    assert lib().limn_b200_sdpa_bwd_kv(one, one, one, one, one, one, None, one, None, 0, 1, 4, 4, 8, 8, 0, 1.0, None) == 1
+    # an empty batch is a successful no-op
+    assert fwd(one, one, one, None, one, one, 0, 0, 4, 4, 8, 8, 0, 1.0, None) == 0 and err() == ""
+
+
+def test_dispatch_policy():
+    from limn_b200._lib import PATH_GENERAL, PATH_TCGEN05, lib
+
+    path = lib().limn_b200_sdpa_path
+    # dtype codes: f32 0, f16 1, bf16 2, f64 3
+    assert path(2, 256, 4096, 4096, 128, 128, 1, 0, 128**-0.5) == PATH_TCGEN05
+    assert path(1, 256, 2048, 2048, 64, 64, 0, 0, 0.125) == PATH_TCGEN05
+    assert path(2, 1, 1, 300, 64, 64, 0, 0, 0.125) == PATH_TCGEN05
+    for general in (
+        (0, 2, 128, 128, 32, 32, 1, 0, 32**-0.5),  # float32 computes at its own width
+        (3, 2, 64, 64, 64, 64, 1, 0, 0.125),  # float64
+        (2, 2, 64, 64, 32, 32, 1, 0, 0.2),  # head dim outside {64, 128}
+        (2, 2, 64, 64, 64, 128, 0, 0, 0.125),  # hd != hd_v
+        (2, 2, 64, 64, 64, 64, 0, 1, 0.125),  # key mask
+        (2, 2, 64, 64, 64, 64, 0, 0, -0.125),  # non-positive scale
+    ):
+        assert path(*general) == PATH_GENERAL
+    assert path(2, 2, 64, 65, 64, 64, 1, 0, 0.125) == -1
+
+
+def _nodes(host, dtype, qs, ks, vs, causal, mask=False):
+    q, k, v = (host.Node((), dtype, s) for s in (qs, ks, vs))
+    tail = (host.Node((), dtype, qs[:-2] + ks[-2:-1]),) if mask else ()
+    outs = ((dtype, qs[:-1] + vs[-1:]), (host.accumulate_in(dtype), qs[:-1] + (1,)))
+    return host.custom("sdpa", (q, k, v) + tail, (causal, qs[-1] ** -0.5), outs)
+
+
+def test_builders_read_a_node_like_the_reference_does():
+    from limn_b200 import host, registry
+
+    out, lse = _nodes(host, host.bfloat16, (2, 3, 100, 64), (2, 3, 100, 64), (2, 3, 100, 64), True)
+    assert out.arg.index == 0 and lse.arg.index == 1 and out.srcs is lse.srcs
+    form = registry.Form(out, 3)
+    assert (form.bh, form.t_q, form.t_k, form.hd, form.hd_v, form.causal, form.has_mask) == (6, 100, 100, 64, 64, True, False)
+    assert form.dtype == 2 and form.outputs == 2
+    masked = _nodes(host, host.float32, (40, 8), (72, 8), (72, 12), False, mask=True)[0]
+    form = registry.Form(masked, 3)
+    assert (form.bh, form.t_q, form.t_k, form.hd, form.hd_v, form.has_mask) == (1, 40, 72, 8, 12, True)
+    for name in registry.NAMES:
+        assert callable(registry.BUILDERS[name])
+    run = registry.build_sdpa(out)
+    with pytest.raises(RuntimeError, match="built for 3 inputs and 2 outputs"):
+        run([], [])
+
+
+def test_builders_refuse_what_the_ops_cannot_be():
+    from limn_b200 import host, registry
+
+    with pytest.raises(ValueError, match="square keys"):
+        registry.build_sdpa(_nodes(host, host.float32, (4, 8), (5, 8), (5, 8), True)[0])
+    with pytest.raises(ValueError, match="head dims differ"):
+        registry.build_sdpa(_nodes(host, host.float32, (4, 8), (4, 6), (4, 8), False)[0])
+    int8 = host.DType("int8", 1)
+    with pytest.raises(NotImplementedError, match="int8"):
+        registry.build_sdpa(_nodes(host, int8, (4, 8), (4, 8), (4, 8), False)[0])
+
+
+def test_install_needs_a_registry():
+    import limn_b200
+
+    class Bare:
+        pass
+
+    with pytest.raises(TypeError, match="no CUSTOM registry"):
+        limn_b200.install(Bare())
+
+    class WithRegistry:
+        def __init__(self):
+            self.custom = {}
+
+    dev = limn_b200.install(WithRegistry())
+    assert set(dev.custom) == {"sdpa", "sdpa_bwd_q", "sdpa_bwd_kv"}
+
+
+def test_host_validation_matches_the_frontend_messages():
+    from limn_b200 import host
+
+    z = lambda *s: np.zeros(s, np.float32)
+    with pytest.raises(ValueError, match="2D\\+ tensors"):
+        host._validate(z(8), z(8), z(8), None, False)
+    with pytest.raises(ValueError, match="key counts differ"):
+        host._validate(z(4, 8), z(5, 8), z(6, 8), None, False)
+    with pytest.raises(ValueError, match="one flag per key"):
+        host._validate(z(4, 8), z(5, 8), z(5, 8), z(4), False)
+
+
+@pytest.mark.skipif(not (REFERENCE / "limn").is_dir(), reason="the reference checkout is not on this machine")
+def test_install_into_limns_own_registry_and_plan():
+    """With limn importable: install() on one of its CompiledDevices, then let its frontend,
+    scheduler and plan builder reach our builders with real nodes (nothing is launched)."""
+    sys.path.insert(0, str(REFERENCE))
+    try:
+        import limn
+        from limn import backend_c
+        from limn.ops import Op, topological
+        from limn.tensor import Tensor
+
+        import limn_b200
+        from limn_b200 import registry
+
+        dev = limn_b200.install(backend_c.CDevice())
+        assert all(dev.has_custom(name) for name in registry.NAMES)
+        seen = []
+        for name in registry.NAMES:
+            build = dev.custom[name]
+            dev.custom[name] = lambda node, build=build: (seen.append(registry.Form(node, 3 if node.arg.name == "sdpa" else 6)), build(node))[1]
+        import limn.device as device_module
+
+        original = device_module.DEVICES["c"]
+        device_module.DEVICES["c"] = lambda: dev  # the device set_device("c") hands out
+        limn.set_device("c")
+        rng = np.random.default_rng(0)
+        q, k, v = (Tensor(rng.standard_normal((2, 3, 64, 16)).astype(np.float32), requires_grad=True) for _ in range(3))
+        out = q.attention(k, v, causal=True)
+        grads = limn.grad((out * out).sum(), [q, k, v])
+        nodes = topological([g.node for g in grads])
+        customs = [n for n in nodes if n.op is Op.CUSTOM]
+        assert {n.arg.name for n in customs} == set(registry.NAMES)
+        plan = dev.plan_of(nodes, {n: i for i, n in enumerate(nodes)}, [g.node for g in grads]) if hasattr(dev, "plan_of") else None
+        assert plan is not None
+        assert sorted(f.name for f in seen) == sorted(registry.NAMES), "each kernel is built once per plan (sibling merge)"
+        by_name = {f.name: f for f in seen}
+        assert (by_name["sdpa"].bh, by_name["sdpa"].t_q, by_name["sdpa"].hd, by_name["sdpa"].outputs) == (6, 64, 16, 2)
+        assert by_name["sdpa_bwd_kv"].outputs == 2 and by_name["sdpa_bwd_q"].inputs == 6
+    finally:
+        sys.path.remove(str(REFERENCE))
+        import limn.device as device_module
+
+        device_module.set_device("numpy")
+        if "original" in locals():
+            device_module.DEVICES["c"] = original
