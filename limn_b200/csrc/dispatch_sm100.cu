@@ -4,9 +4,10 @@
 namespace limn_b200 {
 
 int tcgen05_fwd(const Problem& p);
+int tcgen05_bwd_q(const Problem& p);
+int tcgen05_bwd_kv(const Problem& p);
 
 bool tcgen05_serves(Op op, const Problem& p) {
-  if (op != Op::Fwd) return false;
   if (p.dtype != LIMN_B200_BF16 && p.dtype != LIMN_B200_F16) return false;
   if (p.hd != p.hd_v || (p.hd != 64 && p.hd != 128)) return false;
   if (p.mask != nullptr) return false;
@@ -18,7 +19,8 @@ bool tcgen05_serves(Op op, const Problem& p) {
 int tcgen05_launch(Op op, const Problem& p) {
   switch (op) {
     case Op::Fwd: return tcgen05_fwd(p);
-    default: break;
+    case Op::BwdQ: return tcgen05_bwd_q(p);
+    case Op::BwdKV: return tcgen05_bwd_kv(p);
   }
   return fail(LIMN_B200_UNSUPPORTED, "sdpa: no tcgen05 kernel for this op");
 }

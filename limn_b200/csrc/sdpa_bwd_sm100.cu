@@ -1,0 +1,403 @@
+// "sdpa_bwd_q" and "sdpa_bwd_kv" for f16/bf16 with hd == hd_v in {64, 128}: TMA-staged
+// tiles, tcgen05 MMAs accumulating in tensor memory, probabilities rebuilt from the saved
+// log-sum-exp. Two separate passes, as in the kernels these replace (limn/cuda_emit.py:968-1083):
+// every dQ row and every dK/dV row has one owning CTA and is accumulated in a fixed order,
+// so there are no atomics and two runs give the same bits.
+//
+// sdpa_bwd_q: a CTA owns 128 query rows (Q and dO tiles stay in shared memory) and streams
+// key tiles j of 128 keys:
+//     S  = Q K_j^T            (both K-major)            -> tensor memory, fp32
+//     dP = dO V_j^T           (both K-major)            -> tensor memory, fp32
+//     dS = exp2(S*c - L) * (dP - delta)  by 256 threads -> tensor memory, 16-bit, over dP
+//     dQ += dS K_j            (A from tensor memory, B = the same K_j tile read MN-major)
+// sdpa_bwd_kv: a CTA owns 128 keys (K and V tiles stay) and streams query tiles i:
+//     S^T  = K Q_i^T, dP^T = V dO_i^T                   -> tensor memory (keys on the lanes)
+//     P^T, dS^T as above, per-query L and delta read from shared memory
+//     dV += P^T dO_i, dK += dS^T Q_i   (A from tensor memory, B = the streamed tiles MN-major)
+// The scale is applied once to dQ and dK when they are written (oracle: limn/sdpa.py:157-170,
+// :190-203, where ds carries the scale per element; the products are the same up to rounding).
+//
+// Warp roles (10 warps): 0-3 and 4-7 are two groups of 128 threads, thread r of each owning
+// lane r (a query row, or a key row) and each group taking 64 of a tile's 128 columns;
+// warp 8 is the TMA producer, warp 9 issues MMAs and owns tensor memory.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.h"
+#include "sm100_ptx.cuh"
+#include "tensor_map.h"
+
+namespace limn_b200 {
+namespace {
+
+using namespace ptx;
+
+constexpr int kTile = 128;
+constexpr int kThreads = 320;
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr uint32_t kTmemCols = 512;
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int D>
+struct BwdLayout {
+  static constexpr int kTileBytes = kTile * D * 2;
+  static constexpr int kAtomBytes = kTile * 128;
+  static constexpr int kStages = D == 128 ? 2 : 3;
+  static constexpr int kHeldOff = 0;                               // two resident tiles
+  static constexpr int kStreamOff = 2 * kTileBytes;                // kStages pairs of streamed tiles
+  static constexpr int kStatOff = kStreamOff + kStages * 2 * kTileBytes;  // [2 buffers][L, delta][128] floats
+  static constexpr int kBarOff = kStatOff + 2 * 2 * kTile * 4;
+  static constexpr int kBytes = kBarOff + 256 + 1024;
+  // tensor-memory columns
+  static constexpr int kSCol = 0;      // S (or S^T); P^T overlays it as 16-bit
+  static constexpr int kPCol = 128;    // dP (or dP^T); dS overlays it as 16-bit
+  static constexpr int kAcc0 = 256;    // dQ, or dV
+  static constexpr int kAcc1 = 256 + D;  // dK
+};
+
+template <int D>
+struct BwdBars {
+  static constexpr int kS = BwdLayout<D>::kStages;
+  static constexpr int held_full = 0;
+  static constexpr int stream_full = 1;           // + stage
+  static constexpr int stream_empty = 1 + kS;     // + stage
+  static constexpr int s_full = 1 + 2 * kS;       // S and dP ready
+  static constexpr int ds_full = s_full + 1;      // 16-bit operands written (256 arrivals)
+  static constexpr int acc_full = ds_full + 1;
+  static constexpr int count = acc_full + 1;
+};
+
+struct BwdParams {
+  const float* lse;
+  const float* delta;
+  void* out0;   // dQ, or dK
+  void* out1;   // dV
+  unsigned* status;
+  int t_q, t_k;
+  int q_tiles, kv_tiles;
+  float scale;
+};
+
+__device__ __forceinline__ void group_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+// One accumulator row slice (32 fp32 columns) scaled, rounded and written as 64 bytes.
+template <bool kFp16>
+__device__ __forceinline__ void store_row32(void* base, long long elem_offset, const uint32_t (&acc)[32], float mul) {
+  uint4* dst = reinterpret_cast<uint4*>(static_cast<unsigned char*>(base) + elem_offset * 2);
+#pragma unroll
+  for (int v4 = 0; v4 < 4; ++v4) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float a = __uint_as_float(acc[v4 * 8 + 2 * i]) * mul;
+      const float b = __uint_as_float(acc[v4 * 8 + 2 * i + 1]) * mul;
+      w[i] = kFp16 ? pack_f16(a, b) : pack_bf16(a, b);
+    }
+    dst[v4] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+// kKV = false: sdpa_bwd_q (CTA owns query rows, streams K/V). kKV = true: sdpa_bwd_kv.
+template <int D, bool kCausal, bool kFp16, bool kKV>
+__global__ void __launch_bounds__(kThreads, 1)
+sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                const BwdParams prm) {
+  using L = BwdLayout<D>;
+  using B = BwdBars<D>;
+  extern __shared__ unsigned char smem_unaligned[];
+  __shared__ uint32_t tmem_slot;
+  __shared__ uint32_t abort_flag;
+
+  const uint32_t base = (smem_addr(smem_unaligned) + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_unaligned + (base - smem_addr(smem_unaligned));
+  float* stat = reinterpret_cast<float*>(base_ptr + L::kStatOff);
+  const uint32_t bars = base + L::kBarOff;
+  auto bar = [&](int i) { return bars + 8u * i; };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ---- the tile this CTA owns and the range of tiles it streams ----
+  const int own_tiles = kKV ? prm.kv_tiles : prm.q_tiles;
+  const int problem = blockIdx.x / own_tiles;
+  const int slot = blockIdx.x - problem * own_tiles;
+  // longest streams first: under causal the last query tile sees every key tile, the first key tile every query tile
+  const int own = (kCausal && !kKV) ? own_tiles - 1 - slot : slot;
+  const int own0 = own * kTile;
+  int first, count;
+  if (kKV) {
+    first = kCausal ? own : 0;
+    count = prm.q_tiles - first;
+  } else {
+    first = 0;
+    count = kCausal ? min(prm.kv_tiles, own + 1) : prm.kv_tiles;
+  }
+
+  if (threadIdx.x == 0) {
+    abort_flag = *reinterpret_cast<volatile unsigned*>(prm.status) != kStatusOk;
+    for (int i = 0; i < B::count; ++i) mbar_init(bar(i), i == B::ds_full ? 256u : 1u);
+    mbar_init_fence();
+  }
+  __syncthreads();
+  if (abort_flag) return;
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_addr(&tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+
+  // resident tiles: (Q, dO) for the dQ pass, (K, V) for the dK/dV pass; streamed: the other pair
+  const CUtensorMap* held_a = kKV ? &map_k : &map_q;
+  const CUtensorMap* held_b = kKV ? &map_v : &map_do;
+  const CUtensorMap* stream_a = kKV ? &map_q : &map_k;
+  const CUtensorMap* stream_b = kKV ? &map_do : &map_v;
+  const uint32_t held_a_smem = base + L::kHeldOff, held_b_smem = held_a_smem + L::kTileBytes;
+  auto stream_a_smem = [&](int stage) { return base + L::kStreamOff + stage * 2 * L::kTileBytes; };
+  auto stream_b_smem = [&](int stage) { return stream_a_smem(stage) + L::kTileBytes; };
+
+  bool ok = true;
+
+  if (warp == kProducerWarp) {
+    // ================= TMA producer =================
+    if (lane == 0) {
+      tma_prefetch_descriptor(held_a);
+      tma_prefetch_descriptor(held_b);
+      tma_prefetch_descriptor(stream_a);
+      tma_prefetch_descriptor(stream_b);
+      mbar_expect_tx(bar(B::held_full), 2 * L::kTileBytes);
+#pragma unroll
+      for (int a = 0; a < D / 64; ++a) {
+        tma_load_3d(held_a_smem + a * L::kAtomBytes, held_a, bar(B::held_full), a * 64, own0, problem);
+        tma_load_3d(held_b_smem + a * L::kAtomBytes, held_b, bar(B::held_full), a * 64, own0, problem);
+      }
+      for (int it = 0; it < count; ++it) {
+        const int stage = it % L::kStages;
+        const uint32_t wrap = (it / L::kStages) & 1;
+        ok = mbar_wait(bar(B::stream_empty + stage), wrap ^ 1u, prm.status, 0x1100u | stage);
+        if (!ok) break;
+        mbar_expect_tx(bar(B::stream_full + stage), 2 * L::kTileBytes);
+        const int row0 = (first + it) * kTile;
+#pragma unroll
+        for (int a = 0; a < D / 64; ++a) {
+          tma_load_3d(stream_a_smem(stage) + a * L::kAtomBytes, stream_a, bar(B::stream_full + stage), a * 64, row0, problem);
+          tma_load_3d(stream_b_smem(stage) + a * L::kAtomBytes, stream_b, bar(B::stream_full + stage), a * 64, row0, problem);
+        }
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ================= MMA issuer =================
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = mma_idesc(kTile, kTile, kFp16, false, false);
+      constexpr uint32_t idesc_acc = mma_idesc(kTile, D, kFp16, false, true);
+      // C[128 x 128] = A B^T over the head dim, both tiles K-major in shared memory
+      auto issue_nt = [&](uint32_t c_col, uint32_t a_tile, uint32_t b_tile) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * L::kAtomBytes + (kk % 4) * 32;
+          mma_ss(tmem + c_col, smem_desc_sw128(a_tile + off, 0, 1024), smem_desc_sw128(b_tile + off, 0, 1024), idesc_s, kk > 0);
+        }
+      };
+      // C[128 x D] += A B with A 16-bit in tensor memory (two 32-column halves, 64 columns apart) and
+      // B[128 x D] a shared-memory tile read MN-major, 16 of its rows per instruction
+      auto issue_acc = [&](uint32_t c_col, uint32_t a_col, uint32_t b_tile, bool fresh) {
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk)
+          mma_ts(tmem + c_col, tmem + a_col + (kk / 4) * 64 + (kk % 4) * 8,
+                 smem_desc_sw128(b_tile + kk * 16 * 128, L::kAtomBytes, 1024), idesc_acc, !(fresh && kk == 0));
+      };
+      ok = mbar_wait(bar(B::held_full), 0, prm.status, 0x1200u);
+      for (int it = 0; it < count && ok; ++it) {
+        const int stage = it % L::kStages;
+        const uint32_t wrap = (it / L::kStages) & 1;
+        ok = mbar_wait(bar(B::stream_full + stage), wrap, prm.status, 0x1210u | stage);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (kKV) {
+          issue_nt(L::kSCol, held_a_smem, stream_a_smem(stage));  // S^T  = K Q_i^T
+          issue_nt(L::kPCol, held_b_smem, stream_b_smem(stage));  // dP^T = V dO_i^T
+        } else {
+          issue_nt(L::kSCol, held_a_smem, stream_a_smem(stage));  // S  = Q K_j^T
+          issue_nt(L::kPCol, held_b_smem, stream_b_smem(stage));  // dP = dO V_j^T
+        }
+        mma_commit(bar(B::s_full));
+        ok = mbar_wait(bar(B::ds_full), it & 1, prm.status, 0x1220u);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (kKV) {
+          issue_acc(L::kAcc0, L::kSCol, stream_b_smem(stage), it == 0);  // dV += P^T dO_i
+          issue_acc(L::kAcc1, L::kPCol, stream_a_smem(stage), it == 0);  // dK += dS^T Q_i
+        } else {
+          issue_acc(L::kAcc0, L::kPCol, stream_a_smem(stage), it == 0);  // dQ += dS K_j
+        }
+        mma_commit(bar(B::stream_empty + stage));
+      }
+      if (ok) mma_commit(bar(B::acc_full));
+    }
+  } else {
+    // ================= elementwise stage + epilogue: 2 groups x 128 threads =================
+    const int group = warp >> 2;             // which 64 of a tile's 128 columns
+    const int r = threadIdx.x & 127;         // lane of tensor memory: query row (dQ pass) or key row (dK/dV pass)
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t t_s = tmem + lane_base + L::kSCol;
+    const uint32_t t_p = tmem + lane_base + L::kPCol;
+    const float sl2 = prm.scale * kLog2e;
+    const long long stat_base = static_cast<long long>(problem) * prm.t_q;
+    // dQ pass: this thread's own row statistics live in registers
+    float row_l2 = 0.f, row_delta = 0.f;
+    if (!kKV) {
+      const bool in = own0 + r < prm.t_q;
+      row_l2 = in ? prm.lse[stat_base + own0 + r] * kLog2e : INFINITY;
+      row_delta = in ? prm.delta[stat_base + own0 + r] : 0.f;
+    }
+    for (int it = 0; it < count; ++it) {
+      const int other0 = (first + it) * kTile;  // first key (dQ pass) or first query (dK/dV pass) of the streamed tile
+      float* st = stat + (it & 1) * 2 * kTile;
+      if (kKV) {
+        // per-query statistics of the streamed tile -> shared memory, one value per thread
+        const int which = threadIdx.x >> 7, idx = threadIdx.x & 127;
+        const bool in = other0 + idx < prm.t_q;
+        float val;
+        if (which == 0) val = in ? prm.lse[stat_base + other0 + idx] * kLog2e : INFINITY;
+        else val = in ? prm.delta[stat_base + other0 + idx] : 0.f;
+        st[which * kTile + idx] = val;
+        group_barrier();  // every thread reaches this every iteration, whatever `ok` is
+      }
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full), it & 1, prm.status, 0x1300u));
+      if (!ok) continue;
+      tc_fence_after_sync();
+      // which (lane, column) pairs take part: causal diagonal tile, and keys past t_k in the dQ pass
+      const bool diagonal = kCausal && other0 == own0;
+      const bool ragged = !kKV && other0 + kTile > prm.t_k;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int col0 = group * 64 + c * 32;
+        uint32_t s[32], dp[32];
+        tmem_ld32(t_s + col0, s);
+        tmem_ld32(t_p + col0, dp);
+        tmem_ld_wait();
+        uint32_t p_packed[16], ds_packed[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float pv[2], dsv[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int col = col0 + e + u;
+            float l2, dl;
+            if (kKV) {
+              l2 = st[col];
+              dl = st[kTile + col];
+            } else {
+              l2 = row_l2;
+              dl = row_delta;
+            }
+            float sv = __uint_as_float(s[e + u]);
+            bool hidden = false;
+            if (diagonal) hidden = kKV ? (col < r) : (col > r);   // key index must not exceed query index
+            if (ragged) hidden = hidden || (other0 + col >= prm.t_k);
+            const float p = hidden ? 0.f : exp2_approx(fmaf(sv, sl2, -l2));
+            pv[u] = p;
+            dsv[u] = p * (__uint_as_float(dp[e + u]) - dl);
+          }
+          p_packed[e >> 1] = kFp16 ? pack_f16(pv[0], pv[1]) : pack_bf16(pv[0], pv[1]);
+          ds_packed[e >> 1] = kFp16 ? pack_f16(dsv[0], dsv[1]) : pack_bf16(dsv[0], dsv[1]);
+        }
+        if (kKV) tmem_st16(t_s + group * 64 + c * 16, p_packed);
+        tmem_st16(t_p + group * 64 + c * 16, ds_packed);
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      mbar_arrive(bar(B::ds_full));
+    }
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::acc_full), 0, prm.status, 0x1310u));
+    if (ok) {
+      tc_fence_after_sync();
+      const int row = own0 + r;
+      if (kKV) {
+        // group 0 writes this key's dV row, group 1 its dK row
+        const bool in = row < prm.t_k;
+        const long long out_row = static_cast<long long>(problem) * prm.t_k + row;
+        const uint32_t t_acc = tmem + lane_base + (group == 0 ? L::kAcc0 : L::kAcc1);
+        void* dst = group == 0 ? prm.out1 : prm.out0;
+        const float mul = group == 0 ? 1.f : prm.scale;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t acc[32];
+          tmem_ld32(t_acc + 32 * c, acc);
+          tmem_ld_wait();
+          if (in) store_row32<kFp16>(dst, out_row * D + 32 * c, acc, mul);
+        }
+      } else {
+        // each group writes half of this query's dQ row
+        const bool in = row < prm.t_q;
+        const long long out_row = static_cast<long long>(problem) * prm.t_q + row;
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          const int col = group * (D / 2) + 32 * c;
+          uint32_t acc[32];
+          tmem_ld32(tmem + lane_base + L::kAcc0 + col, acc);
+          tmem_ld_wait();
+          if (in) store_row32<kFp16>(prm.out0, out_row * D + col, acc, prm.scale);
+        }
+      }
+    }
+  }
+
+  // ---- teardown ----
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    if (*reinterpret_cast<volatile unsigned*>(prm.status) != kStatusOk) {
+      for (int i = 0; i < 2000; ++i) __nanosleep(1000);  // let copies and MMAs still in flight land
+    }
+    tc_fence_after_sync();
+    tmem_free(tmem, kTmemCols);
+  }
+}
+
+template <int D, bool kCausal, bool kFp16, bool kKV>
+int launch_bwd(const Problem& p) {
+  using L = BwdLayout<D>;
+  CUtensorMap map_q, map_k, map_v, map_do;
+  if (int rc = make_tile_map(&map_q, p.q, kFp16, p.bh, p.t_q, D, kTile)) return rc;
+  if (int rc = make_tile_map(&map_k, p.k, kFp16, p.bh, p.t_k, D, kTile)) return rc;
+  if (int rc = make_tile_map(&map_v, p.v, kFp16, p.bh, p.t_k, D, kTile)) return rc;
+  if (int rc = make_tile_map(&map_do, p.dout, kFp16, p.bh, p.t_q, D, kTile)) return rc;
+  BwdParams prm;
+  prm.lse = static_cast<const float*>(p.lse_in);
+  prm.delta = static_cast<const float*>(p.delta);
+  prm.out0 = kKV ? p.dk : p.dq;
+  prm.out1 = kKV ? p.dv : nullptr;
+  if (int rc = status_word(&prm.status)) return rc;
+  prm.t_q = p.t_q, prm.t_k = p.t_k;
+  prm.q_tiles = (p.t_q + kTile - 1) / kTile;
+  prm.kv_tiles = (p.t_k + kTile - 1) / kTile;
+  prm.scale = static_cast<float>(p.scale);
+  const long long ctas = p.bh * (kKV ? prm.kv_tiles : prm.q_tiles);
+  if (ctas > 0x7fffffffLL) return fail(LIMN_B200_UNSUPPORTED, "sdpa backward: %lld CTAs exceed one grid", ctas);
+  auto kernel = sdpa_bwd_kernel<D, kCausal, kFp16, kKV>;
+  LIMN_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes),
+            "sizing shared memory for an sdpa backward kernel");
+  kernel<<<dim3(static_cast<unsigned>(ctas)), dim3(kThreads), L::kBytes, p.stream>>>(map_q, map_k, map_v, map_do, prm);
+  LIMN_CUDA(cudaGetLastError(), "launching an sdpa backward kernel");
+  note_launches(1);
+  return LIMN_B200_OK;
+}
+
+template <int D, bool kKV>
+int launch_bwd_d(const Problem& p) {
+  const bool fp16 = p.dtype == LIMN_B200_F16;
+  if (p.causal) return fp16 ? launch_bwd<D, true, true, kKV>(p) : launch_bwd<D, true, false, kKV>(p);
+  return fp16 ? launch_bwd<D, false, true, kKV>(p) : launch_bwd<D, false, false, kKV>(p);
+}
+
+}  // namespace
+
+int tcgen05_bwd_q(const Problem& p) { return p.hd == 128 ? launch_bwd_d<128, false>(p) : launch_bwd_d<64, false>(p); }
+int tcgen05_bwd_kv(const Problem& p) { return p.hd == 128 ? launch_bwd_d<128, true>(p) : launch_bwd_d<64, true>(p); }
+
+}  // namespace limn_b200

@@ -245,7 +245,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     float m = -INFINITY, l = 0.f;
     const int n = n_kv[t];
     for (int j = 0; j < n; ++j) {
-      ok = mbar_wait(bar(B::s_full + t), j & 1, prm.status, 0x0300u | t);
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full + t), j & 1, prm.status, 0x0300u | t));  // warp-uniform: the tensor-memory ops below are warp-wide
       if (!ok) break;
       tc_fence_after_sync();
       uint32_t s[4][32];
@@ -303,7 +303,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tc_fence_before_sync();
       mbar_arrive(bar(B::p_full + t));
     }
-    if (ok && n > 0) ok = mbar_wait(bar(B::o_full + t), 0, prm.status, 0x0310u | t);
+    if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::o_full + t), 0, prm.status, 0x0310u | t));
     if (ok && n > 0) {
       tc_fence_after_sync();
       const float inv = 1.f / l;
