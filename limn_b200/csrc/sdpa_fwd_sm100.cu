@@ -34,6 +34,8 @@ constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;
 constexpr uint32_t kTmemCols = 512;
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleSlack = 8.f;   // log2 units a row maximum may outgrow its reference before O is rescaled
+constexpr int kPolyPairsOf8 = 3;       // of every 8 pairs of scores, how many take exp2 on the FMA pipe instead of the SFU
 
 template <int D>
 struct FwdLayout {
@@ -242,8 +244,13 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const uint32_t t_s = tmem + lane_base + L::kSCol + t * 128;
     const uint32_t t_o = tmem + lane_base + L::kOCol + t * D;
     const float sl2 = prm.scale * kLog2e;
+    // m is the score (in raw units) the exponentials are measured against. It only moves when the
+    // row maximum has outgrown it by more than kRescaleSlack (in log2 units), so most tiles need no
+    // rescaling of O_t; until then probabilities may reach 2^kRescaleSlack, which fp32 sums and
+    // 16-bit P carry without loss. The result is the same softmax: L = m * scale + log(l).
     float m = -INFINITY, l = 0.f;
     const int n = n_kv[t];
+    const uint64_t sl2_2 = f2_pack(sl2, sl2);
     for (int j = 0; j < n; ++j) {
       ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full + t), j & 1, prm.status, 0x0300u | t));  // warp-uniform: the tensor-memory ops below are warp-wide
       if (!ok) break;
@@ -264,31 +271,51 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           for (int i = 0; i < 32; ++i)
             if (c * 32 + i >= limit) s[c][i] = 0xff800000u;  // -inf
       }
-      float mx = m;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[c][i]));
-      // mx is finite: key 0 of the first tile is visible to every row
-      const float alpha = exp2_approx((m - mx) * sl2);
-      const float shift = -mx * sl2;
-      float sum = 0.f;
-      uint32_t packed[2][32];
+        for (int i = 0; i < 32; i += 2) mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // the first tile always has a visible key (key 0), so mx is finite from the start
+      const bool moves = (mx - m) * sl2 > kRescaleSlack;  // true on the first tile, where m is -inf
+      float alpha = 1.f;
+      if (moves) {
+        alpha = exp2_approx((m - mx) * sl2);
+        m = mx;
+      }
+      const float shift = -m * sl2;
+      const uint64_t shift2 = f2_pack(shift, shift);
+      uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int h = 0; h < 2; ++h) {
+        uint32_t packed[32];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float p0 = exp2_approx(fmaf(__uint_as_float(s[c][i]), sl2, shift));
-          const float p1 = exp2_approx(fmaf(__uint_as_float(s[c][i + 1]), sl2, shift));
-          sum += p0 + p1;
-          packed[c >> 1][(c & 1) * 16 + (i >> 1)] = kFp16 ? pack_f16(p0, p1) : pack_bf16(p0, p1);
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = 2 * h + cc;
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const uint64_t x2 = f2_fma(f2_pack_bits(s[c][i], s[c][i + 1]), sl2_2, shift2);
+            float p0, p1;
+            if (((i >> 1) & 7) < kPolyPairsOf8) {
+              exp2_poly2(x2, p0, p1);
+            } else {
+              f2_unpack(x2, p0, p1);
+              p0 = exp2_approx(p0);
+              p1 = exp2_approx(p1);
+            }
+            sum2[(i >> 1) & 1] = f2_add(sum2[(i >> 1) & 1], f2_pack(p0, p1));
+            packed[cc * 16 + (i >> 1)] = kFp16 ? pack_f16(p0, p1) : pack_bf16(p0, p1);
+          }
         }
-      l = l * alpha + sum;
-      m = mx;
-      tmem_st32(t_s, packed[0]);
-      tmem_st32(t_s + 32, packed[1]);
+        tmem_st32(t_s + 32 * h, packed);
+      }
+      float sum_a, sum_b, sum_c, sum_d;
+      f2_unpack(sum2[0], sum_a, sum_b);
+      f2_unpack(sum2[1], sum_c, sum_d);
+      l = l * alpha + ((sum_a + sum_b) + (sum_c + sum_d));
       // O_t was last written by the PV of tile j-1, which s_full also covers
-      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+      if (j > 0 && __any_sync(0xffffffffu, moves)) {
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           uint32_t o[32];

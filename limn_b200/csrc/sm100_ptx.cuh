@@ -249,5 +249,62 @@ __device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
   return r;
 }
 
+// ---- packed fp32 pairs (one instruction, two lanes of math) ----
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_pack_bits(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
+// 2^x for two values on the FMA pipe instead of the special-function unit: round x to the
+// nearest integer n with the 1.5 * 2^23 trick, evaluate a cubic for 2^(x - n) on [-0.5, 0.5]
+// (max relative error 7.5e-5), and add n into the exponent field. x is clamped at -125 so the
+// exponent stays in the normal range; values that small stand for 0.
+__device__ __forceinline__ void exp2_poly2(uint64_t x2, float& lo, float& hi) {
+  float x0, x1;
+  f2_unpack(x2, x0, x1);
+  x2 = f2_pack(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
+  const uint64_t magic = f2_pack(12582912.f, 12582912.f);
+  const uint64_t t2 = f2_add(x2, magic);
+  const uint64_t n2 = f2_add(t2, f2_pack(-12582912.f, -12582912.f));
+  const uint64_t r2 = f2_fma(n2, f2_pack(-1.f, -1.f), x2);
+  uint64_t p2 = f2_fma(f2_pack(0.0551716685f, 0.0551716685f), r2, f2_pack(0.2426111400f, 0.2426111400f));
+  p2 = f2_fma(p2, r2, f2_pack(0.6932609677f, 0.6932609677f));
+  p2 = f2_fma(p2, r2, f2_pack(0.9999280572f, 0.9999280572f));
+  float t0, t1, p0, p1;
+  f2_unpack(t2, t0, t1);
+  f2_unpack(p2, p0, p1);
+  lo = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  hi = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+}
+
 }  // namespace ptx
 }  // namespace limn_b200
