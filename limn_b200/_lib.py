@@ -7,10 +7,12 @@ use raises. Build it with `python -m limn_b200.build`.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import POINTER, c_char_p, c_double, c_float, c_int, c_longlong, c_uint, c_ulonglong, c_void_p
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "liblimn_b200.so"
+# LIMN_B200_LIBRARY names another build of the same library (a debugging aid: comparing kernel variants)
+LIB_PATH = Path(os.environ.get("LIMN_B200_LIBRARY") or Path(__file__).resolve().parent / "liblimn_b200.so")
 
 # dtype codes of enum limn_b200_dtype, by the names limn's DType carries (limn/ops.py:24-27)
 DTYPE_CODES = {"float32": 0, "float16": 1, "bfloat16": 2, "float64": 3}

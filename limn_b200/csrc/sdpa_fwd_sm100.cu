@@ -35,7 +35,10 @@ constexpr int kMmaWarp = 9;
 constexpr uint32_t kTmemCols = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleSlack = 8.f;   // log2 units a row maximum may outgrow its reference before O is rescaled
-constexpr int kPolyPairsOf8 = 3;       // of every 8 pairs of scores, how many take exp2 on the FMA pipe instead of the SFU
+#ifndef LIMN_POLY_PAIRS
+#define LIMN_POLY_PAIRS 0
+#endif
+constexpr int kPolyPairsOf8 = LIMN_POLY_PAIRS;       // of every 8 pairs of scores, how many take exp2 on the FMA pipe instead of the SFU
 
 template <int D>
 struct FwdLayout {
