@@ -78,6 +78,25 @@ def shard_inputs(workload: str, first: int, count: int, want_do: bool):
     return arrays
 
 
+def shard_range(bh: int, rank: int, world: int) -> tuple[int, int]:
+    """(first problem, count) of rank's contiguous share of bh independent (batch, head) problems."""
+    if bh % world:
+        raise ValueError(f"{bh} (batch, head) problems do not split evenly over {world} ranks")
+    per_rank = bh // world
+    return rank * per_rank, per_rank
+
+
+def reduce_max(value: float, dist, device) -> float:
+    """The slowest rank's time: every multi-GPU number is the max over ranks."""
+    if dist is None or not dist.is_initialized() or dist.get_world_size() == 1:
+        return value
+    import torch
+
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
 def peaks() -> tuple[dict, str]:
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
@@ -294,19 +313,16 @@ def gpu_arm(args) -> None:
         torch.cuda.synchronize()
 
     def max_over_ranks(x: float) -> float:
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        return reduce_max(x, dist if world > 1 else None, device)
 
     workload = args.workload
     b, h, s, d, causal, backward, *_ = WORKLOADS[workload]
     bh = b * h
-    if bh % world:
-        raise SystemExit(f"{bh} (batch, head) problems do not split evenly over {world} ranks")
-    per_rank = bh // world
-    shard = Shard(workload, rank * per_rank, per_rank, torch, device)
+    try:
+        first_problem, per_rank = shard_range(bh, rank, world)
+    except ValueError as err:
+        raise SystemExit(str(err))
+    shard = Shard(workload, first_problem, per_rank, torch, device)
     peak, peak_kind = peaks()
 
     # ---- device-resident throughput ----
@@ -349,7 +365,7 @@ def gpu_arm(args) -> None:
         t0 = torch.cuda.Event(enable_timing=True)
         t1 = torch.cuda.Event(enable_timing=True)
         t0.record()
-        dist.all_gather_into_tensor(whole, shard.out)
+        dist.all_gather_into_tensor(whole.view(torch.bfloat16), shard.out.view(torch.bfloat16))
         t1.record()
         torch.cuda.synchronize()
         gather_ms = max_over_ranks(t0.elapsed_time(t1))

@@ -47,7 +47,7 @@ struct BwdLayout {
   static constexpr int kHeldOff = 0;                               // two resident tiles
   static constexpr int kStreamOff = 2 * kTileBytes;                // kStages pairs of streamed tiles
   static constexpr int kStatOff = kStreamOff + kStages * 2 * kTileBytes;  // [2 buffers][L, delta][128] floats
-  static constexpr int kBarOff = kStatOff + 2 * 2 * kTile * 4;
+  static constexpr int kBarOff = kStatOff + 2 * 2 * kTile * 4;  // statistics: [2 groups][2 buffers][-L, -delta][64]
   static constexpr int kBytes = kBarOff + 256 + 1024;
   // tensor-memory columns
   static constexpr int kSCol = 0;      // S (or S^T); P^T overlays it as 16-bit
@@ -62,9 +62,9 @@ struct BwdBars {
   static constexpr int held_full = 0;
   static constexpr int stream_full = 1;           // + stage
   static constexpr int stream_empty = 1 + kS;     // + stage
-  static constexpr int s_full = 1 + 2 * kS;       // S and dP ready
-  static constexpr int ds_full = s_full + 1;      // 16-bit operands written (256 arrivals)
-  static constexpr int acc_full = ds_full + 1;
+  static constexpr int s_full = 1 + 2 * kS;       // + half: that half's columns of S and dP are ready
+  static constexpr int ds_full = s_full + 2;      // + half: its 16-bit operands are written (128 arrivals)
+  static constexpr int acc_full = ds_full + 2;
   static constexpr int count = acc_full + 1;
 };
 
@@ -79,7 +79,8 @@ struct BwdParams {
   float scale;
 };
 
-__device__ __forceinline__ void group_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+// barrier among the 128 threads of one group (ids 1 and 2; 0 is __syncthreads)
+__device__ __forceinline__ void group_barrier(int group) { asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory"); }
 
 // One accumulator row slice (32 fp32 columns) scaled, rounded and written as 64 bytes.
 template <bool kFp16>
@@ -137,7 +138,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
   if (threadIdx.x == 0) {
     abort_flag = *reinterpret_cast<volatile unsigned*>(prm.status) != kStatusOk;
-    for (int i = 0; i < B::count; ++i) mbar_init(bar(i), i == B::ds_full ? 256u : 1u);
+    for (int i = 0; i < B::count; ++i) mbar_init(bar(i), (i == B::ds_full || i == B::ds_full + 1) ? 128u : 1u);
     mbar_init_fence();
   }
   __syncthreads();
@@ -192,49 +193,73 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   } else if (warp == kMmaWarp) {
     // ================= MMA issuer =================
     if (lane == 0) {
-      constexpr uint32_t idesc_s = mma_idesc(kTile, kTile, kFp16, false, false);
+      constexpr uint32_t idesc_s = mma_idesc(kTile, kTile / 2, kFp16, false, false);
       constexpr uint32_t idesc_acc = mma_idesc(kTile, D, kFp16, false, true);
-      // C[128 x 128] = A B^T over the head dim, both tiles K-major in shared memory
-      auto issue_nt = [&](uint32_t c_col, uint32_t a_tile, uint32_t b_tile) {
+      // One half (64 columns) of S and of dP for the streamed tile in `stage`: C[128 x 64] = A B^T over the
+      // head dim, A a resident tile, B rows [64 half, 64 half + 64) of a streamed tile, both K-major.
+      auto issue_scores = [&](int half, int stage) {
+        const uint32_t b_row = half * 64 * 128;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * L::kAtomBytes + (kk % 4) * 32;
-          mma_ss(tmem + c_col, smem_desc_sw128(a_tile + off, 0, 1024), smem_desc_sw128(b_tile + off, 0, 1024), idesc_s, kk > 0);
+          mma_ss(tmem + L::kSCol + half * 64, smem_desc_sw128(held_a_smem + off, 0, 1024),
+                 smem_desc_sw128(stream_a_smem(stage) + b_row + off, 0, 1024), idesc_s, kk > 0);
         }
-      };
-      // C[128 x D] += A B with A 16-bit in tensor memory (two 32-column halves, 64 columns apart) and
-      // B[128 x D] a shared-memory tile read MN-major, 16 of its rows per instruction
-      auto issue_acc = [&](uint32_t c_col, uint32_t a_col, uint32_t b_tile, bool fresh) {
 #pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk)
-          mma_ts(tmem + c_col, tmem + a_col + (kk / 4) * 64 + (kk % 4) * 8,
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * L::kAtomBytes + (kk % 4) * 32;
+          mma_ss(tmem + L::kPCol + half * 64, smem_desc_sw128(held_b_smem + off, 0, 1024),
+                 smem_desc_sw128(stream_b_smem(stage) + b_row + off, 0, 1024), idesc_s, kk > 0);
+        }
+        mma_commit(bar(B::s_full + half));
+      };
+      // C[128 x D] += A B over 64 rows of a streamed tile: A 16-bit in tensor memory at a_col + 64 half
+      // (32 columns), B rows [64 half, +64) of the tile read MN-major, 16 rows per instruction.
+      auto issue_acc = [&](uint32_t c_col, uint32_t a_col, uint32_t b_tile, int half, bool fresh) {
+#pragma unroll
+        for (int kk = 4 * half; kk < 4 * half + 4; ++kk)
+          mma_ts(tmem + c_col, tmem + a_col + half * 64 + (kk % 4) * 8,
                  smem_desc_sw128(b_tile + kk * 16 * 128, L::kAtomBytes, 1024), idesc_acc, !(fresh && kk == 0));
       };
+      auto issue_products = [&](int half, int stage, bool fresh) {
+        if (kKV) {
+          issue_acc(L::kAcc0, L::kSCol, stream_b_smem(stage), half, fresh);  // dV += P^T dO_i
+          issue_acc(L::kAcc1, L::kPCol, stream_a_smem(stage), half, fresh);  // dK += dS^T Q_i
+        } else {
+          issue_acc(L::kAcc0, L::kPCol, stream_a_smem(stage), half, fresh);  // dQ += dS K_j
+        }
+      };
       ok = mbar_wait(bar(B::held_full), 0, prm.status, 0x1200u);
+      if (ok) ok = mbar_wait(bar(B::stream_full + 0), 0, prm.status, 0x1210u);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_scores(0, 0);
+        issue_scores(1, 0);
+      }
+      // Steady state, per streamed tile: as soon as a half's 16-bit operands are back, its products are
+      // issued and then the same half of the next tile's scores, so the other half's elementwise work
+      // always has MMAs running beside it.
       for (int it = 0; it < count && ok; ++it) {
         const int stage = it % L::kStages;
-        const uint32_t wrap = (it / L::kStages) & 1;
-        ok = mbar_wait(bar(B::stream_full + stage), wrap, prm.status, 0x1210u | stage);
-        if (!ok) break;
-        tc_fence_after_sync();
-        if (kKV) {
-          issue_nt(L::kSCol, held_a_smem, stream_a_smem(stage));  // S^T  = K Q_i^T
-          issue_nt(L::kPCol, held_b_smem, stream_b_smem(stage));  // dP^T = V dO_i^T
-        } else {
-          issue_nt(L::kSCol, held_a_smem, stream_a_smem(stage));  // S  = Q K_j^T
-          issue_nt(L::kPCol, held_b_smem, stream_b_smem(stage));  // dP = dO V_j^T
+        const int next = (it + 1) % L::kStages;
+        const uint32_t next_wrap = ((it + 1) / L::kStages) & 1;
+        const bool more = it + 1 < count;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          ok = mbar_wait(bar(B::ds_full + half), it & 1, prm.status, 0x1220u | half);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_products(half, stage, it == 0 && half == 0);
+          if (half == 1) mma_commit(bar(B::stream_empty + stage));
+          if (more) {
+            if (half == 0) {
+              ok = mbar_wait(bar(B::stream_full + next), next_wrap, prm.status, 0x1230u | next);
+              if (!ok) break;
+              tc_fence_after_sync();
+            }
+            issue_scores(half, next);
+          }
         }
-        mma_commit(bar(B::s_full));
-        ok = mbar_wait(bar(B::ds_full), it & 1, prm.status, 0x1220u);
-        if (!ok) break;
-        tc_fence_after_sync();
-        if (kKV) {
-          issue_acc(L::kAcc0, L::kSCol, stream_b_smem(stage), it == 0);  // dV += P^T dO_i
-          issue_acc(L::kAcc1, L::kPCol, stream_a_smem(stage), it == 0);  // dK += dS^T Q_i
-        } else {
-          issue_acc(L::kAcc0, L::kPCol, stream_a_smem(stage), it == 0);  // dQ += dS K_j
-        }
-        mma_commit(bar(B::stream_empty + stage));
       }
       if (ok) mma_commit(bar(B::acc_full));
     }
@@ -246,28 +271,34 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const uint32_t t_s = tmem + lane_base + L::kSCol;
     const uint32_t t_p = tmem + lane_base + L::kPCol;
     const float sl2 = prm.scale * kLog2e;
+    const uint64_t sl2_2 = f2_pack(sl2, sl2);
     const long long stat_base = static_cast<long long>(problem) * prm.t_q;
-    // dQ pass: this thread's own row statistics live in registers
-    float row_l2 = 0.f, row_delta = 0.f;
+    // statistics enter negated: x = s * c + (-L log2e), t = dP + (-delta). A row or column past t_q
+    // gets -L = -inf, which makes its probability exactly 0.
+    uint64_t row_neg_l2 = 0, row_neg_delta = 0;
     if (!kKV) {
       const bool in = own0 + r < prm.t_q;
-      row_l2 = in ? prm.lse[stat_base + own0 + r] * kLog2e : INFINITY;
-      row_delta = in ? prm.delta[stat_base + own0 + r] : 0.f;
+      const float nl = in ? -prm.lse[stat_base + own0 + r] * kLog2e : -INFINITY;
+      const float nd = in ? -prm.delta[stat_base + own0 + r] : 0.f;
+      row_neg_l2 = f2_pack(nl, nl);
+      row_neg_delta = f2_pack(nd, nd);
     }
     for (int it = 0; it < count; ++it) {
       const int other0 = (first + it) * kTile;  // first key (dQ pass) or first query (dK/dV pass) of the streamed tile
-      float* st = stat + (it & 1) * 2 * kTile;
+      // per group: [2 buffers][-L log2e, -delta][64 columns]
+      float* st = stat + group * (2 * 2 * 64) + (it & 1) * (2 * 64);
       if (kKV) {
-        // per-query statistics of the streamed tile -> shared memory, one value per thread
-        const int which = threadIdx.x >> 7, idx = threadIdx.x & 127;
-        const bool in = other0 + idx < prm.t_q;
+        // per-query statistics of this group's 64 columns -> shared memory, one value per thread
+        const int which = r >> 6, idx = r & 63;
+        const int query = other0 + group * 64 + idx;
+        const bool in = query < prm.t_q;
         float val;
-        if (which == 0) val = in ? prm.lse[stat_base + other0 + idx] * kLog2e : INFINITY;
-        else val = in ? prm.delta[stat_base + other0 + idx] : 0.f;
-        st[which * kTile + idx] = val;
-        group_barrier();  // every thread reaches this every iteration, whatever `ok` is
+        if (which == 0) val = in ? -prm.lse[stat_base + query] * kLog2e : -INFINITY;
+        else val = in ? -prm.delta[stat_base + query] : 0.f;
+        st[which * 64 + idx] = val;
+        group_barrier(group);  // every thread of the group reaches this every iteration, whatever `ok` is
       }
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full), it & 1, prm.status, 0x1300u));
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full + group), it & 1, prm.status, 0x1300u | group));
       if (!ok) continue;
       tc_fence_after_sync();
       // which (lane, column) pairs take part: causal diagonal tile, and keys past t_k in the dQ pass
@@ -280,38 +311,43 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tmem_ld32(t_s + col0, s);
         tmem_ld32(t_p + col0, dp);
         tmem_ld_wait();
+        if (diagonal || ragged) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int col = col0 + e;
+            bool hidden = false;
+            if (diagonal) hidden = kKV ? (col < r) : (col > r);   // a key index must not exceed the query index
+            if (ragged) hidden = hidden || (other0 + col >= prm.t_k);
+            if (hidden) s[e] = 0xff800000u;  // -inf: the probability becomes exactly 0
+          }
+        }
         uint32_t p_packed[16], ds_packed[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          float pv[2], dsv[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = col0 + e + u;
-            float l2, dl;
-            if (kKV) {
-              l2 = st[col];
-              dl = st[kTile + col];
-            } else {
-              l2 = row_l2;
-              dl = row_delta;
-            }
-            float sv = __uint_as_float(s[e + u]);
-            bool hidden = false;
-            if (diagonal) hidden = kKV ? (col < r) : (col > r);   // key index must not exceed query index
-            if (ragged) hidden = hidden || (other0 + col >= prm.t_k);
-            const float p = hidden ? 0.f : exp2_approx(fmaf(sv, sl2, -l2));
-            pv[u] = p;
-            dsv[u] = p * (__uint_as_float(dp[e + u]) - dl);
+          uint64_t neg_l2, neg_delta;
+          if (kKV) {
+            const float2 a = *reinterpret_cast<const float2*>(st + c * 32 + e);
+            const float2 b = *reinterpret_cast<const float2*>(st + 64 + c * 32 + e);
+            neg_l2 = f2_pack(a.x, a.y);
+            neg_delta = f2_pack(b.x, b.y);
+          } else {
+            neg_l2 = row_neg_l2;
+            neg_delta = row_neg_delta;
           }
-          p_packed[e >> 1] = kFp16 ? pack_f16(pv[0], pv[1]) : pack_bf16(pv[0], pv[1]);
-          ds_packed[e >> 1] = kFp16 ? pack_f16(dsv[0], dsv[1]) : pack_bf16(dsv[0], dsv[1]);
+          float x0, x1;
+          f2_unpack(f2_fma(f2_pack_bits(s[e], s[e + 1]), sl2_2, neg_l2), x0, x1);
+          const float p0 = exp2_approx(x0), p1 = exp2_approx(x1);
+          float d0, d1;
+          f2_unpack(f2_mul(f2_pack(p0, p1), f2_add(f2_pack_bits(dp[e], dp[e + 1]), neg_delta)), d0, d1);
+          if (kKV) p_packed[e >> 1] = kFp16 ? pack_f16(p0, p1) : pack_bf16(p0, p1);
+          ds_packed[e >> 1] = kFp16 ? pack_f16(d0, d1) : pack_bf16(d0, d1);
         }
         if (kKV) tmem_st16(t_s + group * 64 + c * 16, p_packed);
         tmem_st16(t_p + group * 64 + c * 16, ds_packed);
       }
       tmem_st_wait();
       tc_fence_before_sync();
-      mbar_arrive(bar(B::ds_full));
+      mbar_arrive(bar(B::ds_full + group));
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::acc_full), 0, prm.status, 0x1310u));
     if (ok) {
