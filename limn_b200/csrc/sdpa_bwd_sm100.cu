@@ -199,27 +199,33 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // head dim, A a resident tile, B rows [64 half, 64 half + 64) of a streamed tile, both K-major.
       auto issue_scores = [&](int half, int stage) {
         const uint32_t b_row = half * 64 * 128;
+        constexpr uint32_t kAtom16 = L::kAtomBytes >> 4;
+        const uint32_t a0 = desc_lo(held_a_smem, 0), b0 = desc_lo(stream_a_smem(stage) + b_row, 0);
+        const uint32_t a1 = desc_lo(held_b_smem, 0), b1 = desc_lo(stream_b_smem(stage) + b_row, 0);
+        const uint32_t c0 = tmem + L::kSCol + half * 64, c1 = tmem + L::kPCol + half * 64;
+        mma_ss_lo<false>(c0, a0, b0, idesc_s);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * L::kAtomBytes + (kk % 4) * 32;
-          mma_ss(tmem + L::kSCol + half * 64, smem_desc_sw128(held_a_smem + off, 0, 1024),
-                 smem_desc_sw128(stream_a_smem(stage) + b_row + off, 0, 1024), idesc_s, kk > 0);
+        for (int kk = 1; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * kAtom16 + (kk % 4) * 2;  // in 16-byte units
+          mma_ss_lo<true>(c0, a0 + off, b0 + off, idesc_s);
         }
+        mma_ss_lo<false>(c1, a1, b1, idesc_s);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * L::kAtomBytes + (kk % 4) * 32;
-          mma_ss(tmem + L::kPCol + half * 64, smem_desc_sw128(held_b_smem + off, 0, 1024),
-                 smem_desc_sw128(stream_b_smem(stage) + b_row + off, 0, 1024), idesc_s, kk > 0);
+        for (int kk = 1; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * kAtom16 + (kk % 4) * 2;
+          mma_ss_lo<true>(c1, a1 + off, b1 + off, idesc_s);
         }
         mma_commit(bar(B::s_full + half));
       };
       // C[128 x D] += A B over 64 rows of a streamed tile: A 16-bit in tensor memory at a_col + 64 half
       // (32 columns), B rows [64 half, +64) of the tile read MN-major, 16 rows per instruction.
       auto issue_acc = [&](uint32_t c_col, uint32_t a_col, uint32_t b_tile, int half, bool fresh) {
+        const uint32_t b_lo = desc_lo(b_tile + half * 64 * 128, L::kAtomBytes);
+        const uint32_t a = tmem + a_col + half * 64;
+        const uint32_t c = tmem + c_col;
 #pragma unroll
-        for (int kk = 4 * half; kk < 4 * half + 4; ++kk)
-          mma_ts(tmem + c_col, tmem + a_col + half * 64 + (kk % 4) * 8,
-                 smem_desc_sw128(b_tile + kk * 16 * 128, L::kAtomBytes, 1024), idesc_acc, !(fresh && kk == 0));
+        for (int kk = 0; kk < 4; ++kk)
+          mma_ts_lo(c, a + kk * 8, b_lo + kk * (16 * 128 / 16), idesc_acc, (kk > 0 || !fresh) ? 1u : 0u);
       };
       auto issue_products = [&](int half, int stage, bool fresh) {
         if (kKV) {

@@ -175,22 +175,25 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       constexpr uint32_t idesc_pv = mma_idesc(kTileRows, D, kFp16, false, true);
       // S_t = Q_t K^T over the head dim, 16 elements per instruction
       auto issue_s = [&](int t, int stage) {
-        const uint32_t q_tile = base + L::kQOff + t * L::kTileBytes;
-        const uint32_t k_tile = base + L::kKOff + stage * L::kTileBytes;
+        const uint32_t q_lo = desc_lo(base + L::kQOff + t * L::kTileBytes, 0);
+        const uint32_t k_lo = desc_lo(base + L::kKOff + stage * L::kTileBytes, 0);
+        const uint32_t c = tmem + L::kSCol + t * 128;
+        mma_ss_lo<false>(c, q_lo, k_lo, idesc_s);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * L::kAtomBytes + (kk % 4) * 32;
-          mma_ss(tmem + L::kSCol + t * 128, smem_desc_sw128(q_tile + off, 0, 1024), smem_desc_sw128(k_tile + off, 0, 1024),
-                 idesc_s, kk > 0);
+        for (int kk = 1; kk < D / 16; ++kk) {
+          constexpr uint32_t kAtom16 = L::kAtomBytes >> 4;
+          const uint32_t off = (kk / 4) * kAtom16 + (kk % 4) * 2;  // in 16-byte units
+          mma_ss_lo<true>(c, q_lo + off, k_lo + off, idesc_s);
         }
       };
       // O_t += P_t V over the 128 keys of the tile, 16 keys per instruction
       auto issue_pv = [&](int t, int stage, bool first) {
-        const uint32_t v_tile = base + L::kVOff + stage * L::kTileBytes;
+        const uint32_t v_lo = desc_lo(base + L::kVOff + stage * L::kTileBytes, L::kAtomBytes);
+        const uint32_t c = tmem + L::kOCol + t * D;
+        const uint32_t a = tmem + L::kSCol + t * 128;
 #pragma unroll
         for (int kk = 0; kk < kTileRows / 16; ++kk)
-          mma_ts(tmem + L::kOCol + t * D, tmem + L::kSCol + t * 128 + kk * 8,
-                 smem_desc_sw128(v_tile + kk * 16 * 128, L::kAtomBytes, 1024), idesc_pv, !(first && kk == 0));
+          mma_ts_lo(c, a + kk * 8, v_lo + kk * (16 * 128 / 16), idesc_pv, (kk > 0 || !first) ? 1u : 0u);
       };
 #pragma unroll
       for (int t = 0; t < kQTiles; ++t)
