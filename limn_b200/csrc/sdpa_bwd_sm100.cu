@@ -23,6 +23,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "common.h"
 #include "sm100_ptx.cuh"
 #include "tensor_map.h"
@@ -68,7 +70,18 @@ struct BwdBars {
   static constexpr int count = acc_full + 1;
 };
 
+// Build-time diagnostic (-DLIMN_TRACE): one CTA records clock64() at each step of its pipeline into a
+// buffer named by the LIMN_TRACE_PTR environment variable. Compiled out of the shipped library.
+#ifdef LIMN_TRACE
+#define TRACE_EVENT(code) do { if (blockIdx.x == 7 && lane == 0 && trace_n < 250) { prm.trace[warp * 512 + 2 * trace_n] = clock64(); prm.trace[warp * 512 + 2 * trace_n + 1] = (code); ++trace_n; } } while (0)
+#else
+#define TRACE_EVENT(code) do {} while (0)
+#endif
+
 struct BwdParams {
+#ifdef LIMN_TRACE
+  long long* trace;
+#endif
   const float* lse;
   const float* delta;
   void* out0;   // dQ, or dK
@@ -162,6 +175,10 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   auto stream_b_smem = [&](int stage) { return stream_a_smem(stage) + L::kTileBytes; };
 
   bool ok = true;
+#ifdef LIMN_TRACE
+  int trace_n = 0;
+#endif
+  TRACE_EVENT(0);
 
   if (warp == kProducerWarp) {
     // ================= TMA producer =================
@@ -252,10 +269,13 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const bool more = it + 1 < count;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
+          TRACE_EVENT(100 + half);
           ok = mbar_wait(bar(B::ds_full + half), it & 1, prm.status, 0x1220u | half);
           if (!ok) break;
+          TRACE_EVENT(110 + half);
           tc_fence_after_sync();
           issue_products(half, stage, it == 0 && half == 0);
+          TRACE_EVENT(120 + half);
           if (half == 1) mma_commit(bar(B::stream_empty + stage));
           if (more) {
             if (half == 0) {
@@ -264,6 +284,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
               tc_fence_after_sync();
             }
             issue_scores(half, next);
+            TRACE_EVENT(130 + half);
           }
         }
       }
@@ -304,8 +325,10 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         st[which * 64 + idx] = val;
         group_barrier(group);  // every thread of the group reaches this every iteration, whatever `ok` is
       }
+      TRACE_EVENT(1);
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full + group), it & 1, prm.status, 0x1300u | group));
       if (!ok) continue;
+      TRACE_EVENT(2);
       tc_fence_after_sync();
       // which (lane, column) pairs take part: causal diagonal tile, and keys past t_k in the dQ pass
       const bool diagonal = kCausal && other0 == own0;
@@ -317,6 +340,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tmem_ld32(t_s + col0, s);
         tmem_ld32(t_p + col0, dp);
         tmem_ld_wait();
+        TRACE_EVENT(3 + c * 10);
         if (diagonal || ragged) {
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
@@ -350,8 +374,10 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
         if (kKV) tmem_st16(t_s + group * 64 + c * 16, p_packed);
         tmem_st16(t_p + group * 64 + c * 16, ds_packed);
+        TRACE_EVENT(4 + c * 10);
       }
       tmem_st_wait();
+      TRACE_EVENT(5);
       tc_fence_before_sync();
       mbar_arrive(bar(B::ds_full + group));
     }
@@ -418,6 +444,9 @@ int launch_bwd(const Problem& p) {
   prm.t_q = p.t_q, prm.t_k = p.t_k;
   prm.q_tiles = (p.t_q + kTile - 1) / kTile;
   prm.kv_tiles = (p.t_k + kTile - 1) / kTile;
+#ifdef LIMN_TRACE
+  prm.trace = reinterpret_cast<long long*>(strtoull(getenv("LIMN_TRACE_PTR"), nullptr, 16));
+#endif
   prm.scale = static_cast<float>(p.scale);
   const long long ctas = p.bh * (kKV ? prm.kv_tiles : prm.q_tiles);
   if (ctas > 0x7fffffffLL) return fail(LIMN_B200_UNSUPPORTED, "sdpa backward: %lld CTAs exceed one grid", ctas);
