@@ -68,6 +68,24 @@ int limn_b200_sdpa_bwd_kv(const void* q, const void* k, const void* v, const voi
                           int dtype, long long bh, int t_q, int t_k, int hd, int hd_v,
                           int causal, double scale, void* stream);
 
+/* dQ for hosts that must not allocate. No counterpart in the reference: limn's frontend always
+ * brings delta in a buffer of its own (limn/tensor.py:705-707) and its cuda device allocates freely.
+ *   Same result as limn_b200_sdpa_delta followed by limn_b200_sdpa_bwd_q, but delta and the kernels'
+ *   status word live in a fixed array inside the library image instead of in memory somebody has to
+ *   allocate: a host whose own pool holds all device memory, or code that runs where CUDA allocation
+ *   calls are not allowed, passes only inputs and outputs. `out` is the forward's O (bh, t_q, hd_v);
+ *   `status_out` is an optional device word that receives the kernels' status (0 = no wait gave up).
+ *   Limits: bh * t_q <= LIMN_B200_STATIC_MAX_ROWS, else LIMN_B200_UNSUPPORTED and nothing is launched.
+ *   All calls on a device share the array: calls that can overlap on the GPU race and must be
+ *   serialised by the caller. The first call on a device looks the array's address up and should
+ *   come before any stream capture on that device. */
+#define LIMN_B200_STATIC_MAX_ROWS (1LL << 20)
+int limn_b200_sdpa_bwd_q_static(const void* q, const void* k, const void* v, const void* out,
+                                const void* dout, const void* lse, const void* key_mask,
+                                void* dq, unsigned int* status_out,
+                                int dtype, long long bh, int t_q, int t_k, int hd, int hd_v,
+                                int causal, double scale, void* stream);
+
 /* delta = sum_d dout * out per query row, in the statistics dtype: the row dot the frontend
  * computes between the forward and the two backward ops (limn/tensor.py:705-706). Offered so
  * a host that drives the three ops directly need not bring its own reduce kernel. */

@@ -25,6 +25,7 @@ SIGNATURES = {
     "limn_b200_sdpa_fwd": (c_int, (_P, _P, _P, _P, _P, _P) + _SHAPE),
     "limn_b200_sdpa_bwd_q": (c_int, (_P, _P, _P, _P, _P, _P, _P, _P) + _SHAPE),
     "limn_b200_sdpa_bwd_kv": (c_int, (_P, _P, _P, _P, _P, _P, _P, _P, _P) + _SHAPE),
+    "limn_b200_sdpa_bwd_q_static": (c_int, (_P, _P, _P, _P, _P, _P, _P, _P, _P) + _SHAPE),
     "limn_b200_sdpa_delta": (c_int, (_P, _P, _P, c_int, c_longlong, c_int, _P)),
     "limn_b200_sdpa_path": (c_int, (c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_double)),
     "limn_b200_last_launch_count": (c_int, ()),

@@ -96,7 +96,18 @@ int check_problem(const char* name, const Problem& p) {
   return LIMN_B200_OK;
 }
 
-int run(Op op, const char* name, const Problem& p) {
+Problem problem(const void* q, const void* k, const void* v, const void* mask, int dtype, long long bh, int t_q,
+                int t_k, int hd, int hd_v, int causal, double scale, void* stream) {
+  Problem p;
+  p.q = q, p.k = k, p.v = v, p.mask = mask;
+  p.dtype = dtype, p.bh = bh, p.t_q = t_q, p.t_k = t_k, p.hd = hd, p.hd_v = hd_v;
+  p.causal = causal != 0, p.scale = scale, p.stream = static_cast<cudaStream_t>(stream);
+  return p;
+}
+
+}  // namespace
+
+int dispatch_op(Op op, const char* name, const Problem& p) {
   clear_error();
   g_launches = 0;
   if (int rc = check_problem(name, p)) return rc;
@@ -113,16 +124,6 @@ int run(Op op, const char* name, const Problem& p) {
   return general_launch(op, p);
 }
 
-Problem problem(const void* q, const void* k, const void* v, const void* mask, int dtype, long long bh, int t_q,
-                int t_k, int hd, int hd_v, int causal, double scale, void* stream) {
-  Problem p;
-  p.q = q, p.k = k, p.v = v, p.mask = mask;
-  p.dtype = dtype, p.bh = bh, p.t_q = t_q, p.t_k = t_k, p.hd = hd, p.hd_v = hd_v;
-  p.causal = causal != 0, p.scale = scale, p.stream = static_cast<cudaStream_t>(stream);
-  return p;
-}
-
-}  // namespace
 }  // namespace limn_b200
 
 using namespace limn_b200;
@@ -134,7 +135,7 @@ int limn_b200_sdpa_fwd(const void* q, const void* k, const void* v, const void* 
                        void* stream) {
   Problem p = problem(q, k, v, key_mask, dtype, bh, t_q, t_k, hd, hd_v, causal, scale, stream);
   p.out = out, p.lse_out = lse;
-  return run(Op::Fwd, "sdpa", p);
+  return dispatch_op(Op::Fwd, "sdpa", p);
 }
 
 int limn_b200_sdpa_bwd_q(const void* q, const void* k, const void* v, const void* dout, const void* lse,
@@ -142,7 +143,7 @@ int limn_b200_sdpa_bwd_q(const void* q, const void* k, const void* v, const void
                          int hd, int hd_v, int causal, double scale, void* stream) {
   Problem p = problem(q, k, v, key_mask, dtype, bh, t_q, t_k, hd, hd_v, causal, scale, stream);
   p.dout = dout, p.lse_in = lse, p.delta = delta, p.dq = dq;
-  return run(Op::BwdQ, "sdpa_bwd_q", p);
+  return dispatch_op(Op::BwdQ, "sdpa_bwd_q", p);
 }
 
 int limn_b200_sdpa_bwd_kv(const void* q, const void* k, const void* v, const void* dout, const void* lse,
@@ -150,7 +151,7 @@ int limn_b200_sdpa_bwd_kv(const void* q, const void* k, const void* v, const voi
                           int t_k, int hd, int hd_v, int causal, double scale, void* stream) {
   Problem p = problem(q, k, v, key_mask, dtype, bh, t_q, t_k, hd, hd_v, causal, scale, stream);
   p.dout = dout, p.lse_in = lse, p.delta = delta, p.dk = dk, p.dv = dv;
-  return run(Op::BwdKV, "sdpa_bwd_kv", p);
+  return dispatch_op(Op::BwdKV, "sdpa_bwd_kv", p);
 }
 
 int limn_b200_sdpa_delta(const void* out, const void* dout, void* delta, int dtype, long long rows, int hd_v,

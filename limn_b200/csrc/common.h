@@ -31,6 +31,8 @@ struct Problem {
   int causal = 0;
   double scale = 0.0;
   cudaStream_t stream = nullptr;
+  // Where kernels that wait record giving up. Null means the per-device word status_word() allocates.
+  unsigned int* status = nullptr;
 };
 
 enum class Op { Fwd, BwdQ, BwdKV };
@@ -51,6 +53,9 @@ int cuda_fail(cudaError_t err, const char* doing);
 // Device address of the current device's status word (allocated on first use, one per
 // device, zero-initialised). Kernels that wait write a non-zero code there when they give up.
 int status_word(unsigned int** word);
+
+// Argument checks and dispatch shared by every entry point for the three ops.
+int dispatch_op(Op op, const char* name, const Problem& p);
 
 // Kernel families. Each returns a status code and enqueues on p.stream.
 int general_launch(Op op, const Problem& p);

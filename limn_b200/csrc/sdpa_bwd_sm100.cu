@@ -440,7 +440,9 @@ int launch_bwd(const Problem& p) {
   prm.delta = static_cast<const float*>(p.delta);
   prm.out0 = kKV ? p.dk : p.dq;
   prm.out1 = kKV ? p.dv : nullptr;
-  if (int rc = status_word(&prm.status)) return rc;
+  prm.status = p.status;
+  if (prm.status == nullptr)
+    if (int rc = status_word(&prm.status)) return rc;
   prm.t_q = p.t_q, prm.t_k = p.t_k;
   prm.q_tiles = (p.t_q + kTile - 1) / kTile;
   prm.kv_tiles = (p.t_k + kTile - 1) / kTile;

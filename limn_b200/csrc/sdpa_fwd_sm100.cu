@@ -389,7 +389,9 @@ int launch_fwd(const Problem& p) {
   FwdParams prm;
   prm.out = p.out;
   prm.lse = static_cast<float*>(p.lse_out);
-  if (int rc = status_word(&prm.status)) return rc;
+  prm.status = p.status;
+  if (prm.status == nullptr)
+    if (int rc = status_word(&prm.status)) return rc;
   prm.t_q = p.t_q, prm.t_k = p.t_k;
   prm.q_pairs = (p.t_q + kQTiles * kTileRows - 1) / (kQTiles * kTileRows);
   prm.kv_tiles = (p.t_k + kTileRows - 1) / kTileRows;
