@@ -108,18 +108,23 @@ def peaks() -> tuple[dict, str]:
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms while running."""
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 50 ms while running."""
 
-    FIELDS = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    FIELDS = "timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
 
     def __init__(self, index: int):
         self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.marks: list[float] = []
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200"],
+                ["nvidia-smi", "-i", str(index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=self.file, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
+
+    def mark(self) -> None:
+        """Start (first call) or end (second call) of the region whose samples count."""
+        self.marks.append(time.time())
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -128,16 +133,22 @@ class ClockSampler:
         self.proc.terminate()  # the exact process started above
         self.proc.wait()
         self.file.flush()
-        rows = [line.split(",") for line in Path(self.file.name).read_text().splitlines() if line.count(",") >= 5]
+        from datetime import datetime
+
+        rows = [line.split(",") for line in Path(self.file.name).read_text().splitlines() if line.count(",") >= 6]
         os.unlink(self.file.name)
+        lo, hi = (self.marks + [0.0, 1e18])[:2] if len(self.marks) >= 2 else (0.0, 1e18)
         clocks, reasons, top = [], set(), None
         for row in rows:
             try:
-                clocks.append(float(row[0]))
-                top = float(row[1])
+                stamp = datetime.strptime(row[0].strip(), "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                if not (lo - 0.1 <= stamp <= hi + 0.1):
+                    continue
+                clocks.append(float(row[1]))
+                top = float(row[2])
             except ValueError:
                 continue
-            for name, flag in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), row[2:6]):
+            for name, flag in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), row[3:7]):
                 if flag.strip().lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(clocks)) if clocks else None, "sm_max_mhz": top, "reasons": sorted(reasons), "samples": len(clocks)}
@@ -290,6 +301,38 @@ def timed(shard: Shard, steps: int, body) -> float:
     return stop.ms_since(start)
 
 
+def other_workloads(args, main: str, world: int, rank: int, torch, device, barrier, max_over_ranks) -> dict:
+    """The remaining BASELINE configurations, device-resident, forward and (where the workload has one)
+    forward+backward, each timed the same way as the main workload but with fewer steps. They ride along
+    as context for the headline number; the parity of every one of them is the tests' business."""
+    found = {}
+    peak, _ = peaks()
+    tensor_peak = float(peak.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    for name, (b, h, s, d, causal, backward, *_rest) in WORKLOADS.items():
+        if name == main or (b * h) % world:
+            continue
+        first, count = shard_range(b * h, rank, world)
+        shard = Shard(name, first, count, torch, device)
+        steps = max(3, min(args.steps, 10))
+        for _ in range(3):
+            shard.step()
+        barrier()
+        fwd_ms = max_over_ranks(timed(shard, steps, shard.forward)) / steps
+        entry = {"fwd_ms": fwd_ms, "fwd_tflops": fwd_flops(b * h, s, d, causal) / (fwd_ms * 1e-3) / 1e12}
+        entry["fwd_pct_of_measured_peak"] = 100 * entry["fwd_tflops"] / world / tensor_peak
+        if backward:
+            barrier()
+            step_ms = max_over_ranks(timed(shard, steps, shard.step)) / steps
+            entry["fwd_bwd_ms"] = step_ms
+            entry["fwd_bwd_tflops"] = 3.5 * fwd_flops(b * h, s, d, causal) / (step_ms * 1e-3) / 1e12
+            entry["fwd_bwd_pct_of_measured_peak"] = 100 * entry["fwd_bwd_tflops"] / world / tensor_peak
+            entry["includes"] = "sdpa + row dot (delta) + sdpa_bwd_q + sdpa_bwd_kv; credited 3.5x forward flops, executed 4.5x"
+        found[name] = entry
+        del shard
+        torch.cuda.empty_cache()
+    return found
+
+
 def gpu_arm(args) -> None:
     import torch
     import torch.distributed as dist
@@ -322,6 +365,7 @@ def gpu_arm(args) -> None:
         first_problem, per_rank = shard_range(bh, rank, world)
     except ValueError as err:
         raise SystemExit(str(err))
+    sampler = ClockSampler(local) if rank == 0 else None  # started early: nvidia-smi takes a second or two to produce its first row
     shard = Shard(workload, first_problem, per_rank, torch, device)
     peak, peak_kind = peaks()
 
@@ -330,12 +374,12 @@ def gpu_arm(args) -> None:
         shard.step()
     barrier()
     shard.launches = 0
-    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.mark()
     ms = timed(shard, args.steps, shard.step)
     barrier()
     launches = shard.launches
     ms = max_over_ranks(ms)
-    clocks = sampler.stop() if sampler else None
     total_flops = fwd_flops(bh, s, d, causal) * (3.5 if backward else 1.0)
     value = total_flops * args.steps / (ms * 1e-3) / 1e12
 
@@ -356,6 +400,9 @@ def gpu_arm(args) -> None:
 
     e2e_ms = max_over_ranks(timed(shard, e2e_steps, from_host))
     e2e_value = total_flops * e2e_steps / (e2e_ms * 1e-3) / 1e12
+    if sampler:
+        sampler.mark()
+    clocks = sampler.stop() if sampler else None  # samples taken between the first timed launch and the last
 
     # ---- the one collective: gather the output shards (outside the timed region) ----
     gather_ms = None
@@ -369,6 +416,8 @@ def gpu_arm(args) -> None:
         t1.record()
         torch.cuda.synchronize()
         gather_ms = max_over_ranks(t0.elapsed_time(t1))
+
+    others = other_workloads(args, workload, world, rank, torch, device, barrier, max_over_ranks) if args.others else None
 
     status = runtime.device_status()
     if status:
@@ -410,6 +459,7 @@ def gpu_arm(args) -> None:
             "clocks": clocks,
             "gather_ms": gather_ms,
             "parity": parity,
+            "others": others,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -423,6 +473,7 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", choices=("limn_b200", "reference"), default="limn_b200")
     parser.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT_WORKLOAD)
+    parser.add_argument("--no-others", dest="others", action="store_false", help="time only the named workload")
     args = parser.parse_args()
     if args.impl == "reference":
         reference_arm(args)
