@@ -41,30 +41,39 @@ constexpr int kMmaWarp = 9;
 constexpr uint32_t kTmemCols = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 
-template <int D>
+template <int D, bool kKV>
 struct BwdLayout {
   static constexpr int kTileBytes = kTile * D * 2;
   static constexpr int kAtomBytes = kTile * 128;
-  static constexpr int kStages = D == 128 ? 2 : 3;
+  // ring depths of the two streamed tiles. In the dQ pass at head dim 128 the V tile is only read by the
+  // scores and leaves early, so two slots do for it and K gets the third that shared memory has room for.
+  static constexpr int kStagesA = D == 128 ? (kKV ? 2 : 3) : 3;
+  static constexpr int kStagesB = D == 128 ? 2 : 3;
   static constexpr int kHeldOff = 0;                               // two resident tiles
-  static constexpr int kStreamOff = 2 * kTileBytes;                // kStages pairs of streamed tiles
-  static constexpr int kStatOff = kStreamOff + kStages * 2 * kTileBytes;  // [2 buffers][L, delta][128] floats
-  static constexpr int kBarOff = kStatOff + 2 * 2 * kTile * 4;  // statistics: [2 groups][2 buffers][-L, -delta][64]
+  static constexpr int kStreamAOff = 2 * kTileBytes;               // ring of the first streamed tile (K, or Q)
+  static constexpr int kStreamBOff = kStreamAOff + kStagesA * kTileBytes;  // ring of the second (V, or dO)
+  static constexpr int kStatOff = kStreamBOff + kStagesB * kTileBytes;
+  static constexpr int kBarOff = kStatOff + (kKV ? 2 * 2 * kTile * 4 : 0);  // statistics (dK/dV pass only): [2 groups][2 buffers][-L, -delta][64]
   static constexpr int kBytes = kBarOff + 256 + 1024;
+  static_assert(kBytes <= 227 * 1024, "shared memory per CTA");
   // tensor-memory columns
   static constexpr int kSCol = 0;      // S (or S^T); P^T overlays it as 16-bit
   static constexpr int kPCol = 128;    // dP (or dP^T); dS overlays it as 16-bit
   static constexpr int kAcc0 = 256;    // dQ, or dV
   static constexpr int kAcc1 = 256 + D;  // dK
+  static constexpr int kDsCol = 448;     // early schedule: dS (or dS^T) as 16-bit, 64 columns
+  static constexpr int kPtCol = 384;     // early schedule, dK/dV pass at head dim 64: P^T as 16-bit, 64 columns
 };
 
-template <int D>
+template <int D, bool kKV>
 struct BwdBars {
-  static constexpr int kS = BwdLayout<D>::kStages;
+  static constexpr int kSA = BwdLayout<D, kKV>::kStagesA, kSB = BwdLayout<D, kKV>::kStagesB;
   static constexpr int held_full = 0;
-  static constexpr int stream_full = 1;           // + stage
-  static constexpr int stream_empty = 1 + kS;     // + stage
-  static constexpr int s_full = 1 + 2 * kS;       // + half: that half's columns of S and dP are ready
+  static constexpr int a_full = 1;                // + slot
+  static constexpr int a_empty = a_full + kSA;
+  static constexpr int b_full = a_empty + kSA;
+  static constexpr int b_empty = b_full + kSB;
+  static constexpr int s_full = b_empty + kSB;    // + half: that half's columns of S and dP are ready
   static constexpr int ds_full = s_full + 2;      // + half: its 16-bit operands are written (128 arrivals)
   static constexpr int acc_full = ds_full + 2;
   static constexpr int count = acc_full + 1;
@@ -113,13 +122,18 @@ __device__ __forceinline__ void store_row32(void* base, long long elem_offset, c
 }
 
 // kKV = false: sdpa_bwd_q (CTA owns query rows, streams K/V). kKV = true: sdpa_bwd_kv.
-template <int D, bool kCausal, bool kFp16, bool kKV>
+// kEarly picks the schedule. true: the 16-bit operands get tensor-memory columns of their own, so the next
+// tile's full-width (N = 128) scores are issued as soon as this tile's have been read into registers and
+// run beside the elementwise stage; it needs 64 (dQ pass) or 128 (dK/dV pass) spare columns, which the
+// dK/dV pass has only at head dim 64. false: the operands overlay the scores and the tile is pipelined in
+// two 64-column halves instead.
+template <int D, bool kCausal, bool kFp16, bool kKV, bool kEarly>
 __global__ void __launch_bounds__(kThreads, 1)
 sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                 const BwdParams prm) {
-  using L = BwdLayout<D>;
-  using B = BwdBars<D>;
+  using L = BwdLayout<D, kKV>;
+  using B = BwdBars<D, kKV>;
   extern __shared__ unsigned char smem_unaligned[];
   __shared__ uint32_t tmem_slot;
   __shared__ uint32_t abort_flag;
@@ -151,7 +165,16 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
   if (threadIdx.x == 0) {
     abort_flag = *reinterpret_cast<volatile unsigned*>(prm.status) != kStatusOk;
-    for (int i = 0; i < B::count; ++i) mbar_init(bar(i), (i == B::ds_full || i == B::ds_full + 1) ? 128u : 1u);
+    for (int i = 0; i < B::count; ++i) {
+      uint32_t arrivals = 1u;
+      if (kEarly) {
+        // s_full + 1 doubles as "scores read into registers", ds_full + 1 as "products done" (one commit)
+        if (i == B::s_full + 1 || i == B::ds_full) arrivals = 256u;
+      } else if (i == B::ds_full || i == B::ds_full + 1) {
+        arrivals = 128u;
+      }
+      mbar_init(bar(i), arrivals);
+    }
     mbar_init_fence();
   }
   __syncthreads();
@@ -171,8 +194,15 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const CUtensorMap* stream_a = kKV ? &map_q : &map_k;
   const CUtensorMap* stream_b = kKV ? &map_do : &map_v;
   const uint32_t held_a_smem = base + L::kHeldOff, held_b_smem = held_a_smem + L::kTileBytes;
-  auto stream_a_smem = [&](int stage) { return base + L::kStreamOff + stage * 2 * L::kTileBytes; };
-  auto stream_b_smem = [&](int stage) { return stream_a_smem(stage) + L::kTileBytes; };
+  // everything about the rings is keyed by the streamed tile's ordinal `it`
+  auto stream_a_smem = [&](int it) { return base + L::kStreamAOff + (it % L::kStagesA) * L::kTileBytes; };
+  auto stream_b_smem = [&](int it) { return base + L::kStreamBOff + (it % L::kStagesB) * L::kTileBytes; };
+  auto a_full = [&](int it) { return bar(B::a_full + it % L::kStagesA); };
+  auto a_empty = [&](int it) { return bar(B::a_empty + it % L::kStagesA); };
+  auto b_full = [&](int it) { return bar(B::b_full + it % L::kStagesB); };
+  auto b_empty = [&](int it) { return bar(B::b_empty + it % L::kStagesB); };
+  auto a_wrap = [&](int it) { return static_cast<uint32_t>((it / L::kStagesA) & 1); };
+  auto b_wrap = [&](int it) { return static_cast<uint32_t>((it / L::kStagesB) & 1); };
 
   bool ok = true;
 #ifdef LIMN_TRACE
@@ -194,17 +224,19 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tma_load_3d(held_b_smem + a * L::kAtomBytes, held_b, bar(B::held_full), a * 64, own0, problem);
       }
       for (int it = 0; it < count; ++it) {
-        const int stage = it % L::kStages;
-        const uint32_t wrap = (it / L::kStages) & 1;
-        ok = mbar_wait(bar(B::stream_empty + stage), wrap ^ 1u, prm.status, 0x1100u | stage);
-        if (!ok) break;
-        mbar_expect_tx(bar(B::stream_full + stage), 2 * L::kTileBytes);
         const int row0 = (first + it) * kTile;
+        ok = mbar_wait(a_empty(it), a_wrap(it) ^ 1u, prm.status, 0x1100u);
+        if (!ok) break;
+        mbar_expect_tx(a_full(it), L::kTileBytes);
 #pragma unroll
-        for (int a = 0; a < D / 64; ++a) {
-          tma_load_3d(stream_a_smem(stage) + a * L::kAtomBytes, stream_a, bar(B::stream_full + stage), a * 64, row0, problem);
-          tma_load_3d(stream_b_smem(stage) + a * L::kAtomBytes, stream_b, bar(B::stream_full + stage), a * 64, row0, problem);
-        }
+        for (int a = 0; a < D / 64; ++a)
+          tma_load_3d(stream_a_smem(it) + a * L::kAtomBytes, stream_a, a_full(it), a * 64, row0, problem);
+        ok = mbar_wait(b_empty(it), b_wrap(it) ^ 1u, prm.status, 0x1110u);
+        if (!ok) break;
+        mbar_expect_tx(b_full(it), L::kTileBytes);
+#pragma unroll
+        for (int a = 0; a < D / 64; ++a)
+          tma_load_3d(stream_b_smem(it) + a * L::kAtomBytes, stream_b, b_full(it), a * 64, row0, problem);
       }
     }
   } else if (warp == kMmaWarp) {
@@ -252,39 +284,109 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           issue_acc(L::kAcc0, L::kPCol, stream_a_smem(stage), half, fresh);  // dQ += dS K_j
         }
       };
-      ok = mbar_wait(bar(B::held_full), 0, prm.status, 0x1200u);
-      if (ok) ok = mbar_wait(bar(B::stream_full + 0), 0, prm.status, 0x1210u);
-      if (ok) {
-        tc_fence_after_sync();
-        issue_scores(0, 0);
-        issue_scores(1, 0);
-      }
-      // Steady state, per streamed tile: as soon as a half's 16-bit operands are back, its products are
-      // issued and then the same half of the next tile's scores, so the other half's elementwise work
-      // always has MMAs running beside it.
-      for (int it = 0; it < count && ok; ++it) {
-        const int stage = it % L::kStages;
-        const int next = (it + 1) % L::kStages;
-        const uint32_t next_wrap = ((it + 1) / L::kStages) & 1;
-        const bool more = it + 1 < count;
+      if constexpr (kEarly) {
+        constexpr uint32_t idesc_full = mma_idesc(kTile, kTile, kFp16, false, false);
+        constexpr uint32_t kAtom16 = L::kAtomBytes >> 4;
+        // S and dP of the whole streamed tile: C[128 x 128] = A B^T over the head dim
+        auto issue_scores_full = [&](int stage) {
+          const uint32_t a0 = desc_lo(held_a_smem, 0), b0 = desc_lo(stream_a_smem(stage), 0);
+          const uint32_t a1 = desc_lo(held_b_smem, 0), b1 = desc_lo(stream_b_smem(stage), 0);
+          mma_ss_lo<false>(tmem + L::kSCol, a0, b0, idesc_full);
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          TRACE_EVENT(100 + half);
-          ok = mbar_wait(bar(B::ds_full + half), it & 1, prm.status, 0x1220u | half);
-          if (!ok) break;
-          TRACE_EVENT(110 + half);
+          for (int kk = 1; kk < D / 16; ++kk) {
+            const uint32_t off = (kk / 4) * kAtom16 + (kk % 4) * 2;
+            mma_ss_lo<true>(tmem + L::kSCol, a0 + off, b0 + off, idesc_full);
+          }
+          mma_ss_lo<false>(tmem + L::kPCol, a1, b1, idesc_full);
+#pragma unroll
+          for (int kk = 1; kk < D / 16; ++kk) {
+            const uint32_t off = (kk / 4) * kAtom16 + (kk % 4) * 2;
+            mma_ss_lo<true>(tmem + L::kPCol, a1 + off, b1 + off, idesc_full);
+          }
+          mma_commit(bar(B::s_full));
+        };
+        // C[128 x D] += A B over all 128 rows of a streamed tile, A 16-bit in its own 64 columns
+        auto issue_acc_full = [&](uint32_t c_col, uint32_t a_col, uint32_t b_tile, bool fresh) {
+          const uint32_t b_lo = desc_lo(b_tile, L::kAtomBytes);
+#pragma unroll
+          for (int kk = 0; kk < kTile / 16; ++kk)
+            mma_ts_lo(tmem + c_col, tmem + a_col + kk * 8, b_lo + kk * (16 * 128 / 16), idesc_acc, (kk > 0 || !fresh) ? 1u : 0u);
+        };
+        auto wait_tile = [&](int it) {
+          bool got = mbar_wait(a_full(it), a_wrap(it), prm.status, 0x1210u);
+          if (got) got = mbar_wait(b_full(it), b_wrap(it), prm.status, 0x1211u);
+          return got;
+        };
+        ok = mbar_wait(bar(B::held_full), 0, prm.status, 0x1200u);
+        if (ok) ok = wait_tile(0);
+        if (ok) {
           tc_fence_after_sync();
-          issue_products(half, stage, it == 0 && half == 0);
-          TRACE_EVENT(120 + half);
-          if (half == 1) mma_commit(bar(B::stream_empty + stage));
-          if (more) {
-            if (half == 0) {
-              ok = mbar_wait(bar(B::stream_full + next), next_wrap, prm.status, 0x1230u | next);
-              if (!ok) break;
-              tc_fence_after_sync();
+          issue_scores_full(0);
+          if (!kKV) mma_commit(b_empty(0));  // dQ pass: V is read by the scores only
+        }
+        for (int it = 0; it < count && ok; ++it) {
+          if (it + 1 < count) {
+            // the next tile's scores may overwrite this tile's once every thread holds them in registers
+            ok = mbar_wait(bar(B::s_full + 1), it & 1, prm.status, 0x1240u);
+            if (ok) ok = wait_tile(it + 1);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_scores_full(it + 1);
+            if (!kKV) mma_commit(b_empty(it + 1));
+          }
+          ok = mbar_wait(bar(B::ds_full), it & 1, prm.status, 0x1220u);
+          if (!ok) break;
+          tc_fence_after_sync();
+          if (kKV) {
+            issue_acc_full(L::kAcc0, L::kPtCol, stream_b_smem(it), it == 0);  // dV += P^T dO_i
+            issue_acc_full(L::kAcc1, L::kDsCol, stream_a_smem(it), it == 0);  // dK += dS^T Q_i
+          } else {
+            issue_acc_full(L::kAcc0, L::kDsCol, stream_a_smem(it), it == 0);  // dQ += dS K_j
+          }
+          mma_commit(bar(B::ds_full + 1));            // products done: the operand columns may be rewritten
+          mma_commit(a_empty(it));
+          if (kKV) mma_commit(b_empty(it));
+        }
+      } else {
+        auto wait_tile = [&](int it) {
+          bool got = mbar_wait(a_full(it), a_wrap(it), prm.status, 0x1210u);
+          if (got) got = mbar_wait(b_full(it), b_wrap(it), prm.status, 0x1211u);
+          return got;
+        };
+        ok = mbar_wait(bar(B::held_full), 0, prm.status, 0x1200u);
+        if (ok) ok = wait_tile(0);
+        if (ok) {
+          tc_fence_after_sync();
+          issue_scores(0, 0);
+          issue_scores(1, 0);
+        }
+        // Steady state, per streamed tile: as soon as a half's 16-bit operands are back, its products are
+        // issued and then the same half of the next tile's scores, so the other half's elementwise work
+        // always has MMAs running beside it.
+        for (int it = 0; it < count && ok; ++it) {
+          const bool more = it + 1 < count;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            TRACE_EVENT(100 + half);
+            ok = mbar_wait(bar(B::ds_full + half), it & 1, prm.status, 0x1220u | half);
+            if (!ok) break;
+            TRACE_EVENT(110 + half);
+            tc_fence_after_sync();
+            issue_products(half, it, it == 0 && half == 0);
+            TRACE_EVENT(120 + half);
+            if (half == 1) {
+              mma_commit(a_empty(it));
+              mma_commit(b_empty(it));
             }
-            issue_scores(half, next);
-            TRACE_EVENT(130 + half);
+            if (more) {
+              if (half == 0) {
+                ok = wait_tile(it + 1);
+                if (!ok) break;
+                tc_fence_after_sync();
+              }
+              issue_scores(half, it + 1);
+              TRACE_EVENT(130 + half);
+            }
           }
         }
       }
@@ -325,61 +427,130 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         st[which * 64 + idx] = val;
         group_barrier(group);  // every thread of the group reaches this every iteration, whatever `ok` is
       }
-      TRACE_EVENT(1);
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full + group), it & 1, prm.status, 0x1300u | group));
-      if (!ok) continue;
-      TRACE_EVENT(2);
-      tc_fence_after_sync();
-      // which (lane, column) pairs take part: causal diagonal tile, and keys past t_k in the dQ pass
-      const bool diagonal = kCausal && other0 == own0;
-      const bool ragged = !kKV && other0 + kTile > prm.t_k;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const int col0 = group * 64 + c * 32;
-        uint32_t s[32], dp[32];
-        tmem_ld32(t_s + col0, s);
-        tmem_ld32(t_p + col0, dp);
+      if constexpr (kEarly) {
+        TRACE_EVENT(1);
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full), it & 1, prm.status, 0x1300u | group));
+        if (!ok) continue;
+        TRACE_EVENT(2);
+        tc_fence_after_sync();
+        // this group's 64 columns of S and dP, all into registers, so the tile's tensor memory can be reused
+        uint32_t s[2][32], dp[2][32];
+        tmem_ld32(t_s + group * 64, s[0]);
+        tmem_ld32(t_s + group * 64 + 32, s[1]);
+        tmem_ld32(t_p + group * 64, dp[0]);
+        tmem_ld32(t_p + group * 64 + 32, dp[1]);
         tmem_ld_wait();
-        TRACE_EVENT(3 + c * 10);
+        tc_fence_before_sync();
+        mbar_arrive(bar(B::s_full + 1));
+        TRACE_EVENT(3);
+        const bool diagonal = kCausal && other0 == own0;
+        const bool ragged = !kKV && other0 + kTile > prm.t_k;
         if (diagonal || ragged) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int col = col0 + e;
-            bool hidden = false;
-            if (diagonal) hidden = kKV ? (col < r) : (col > r);   // a key index must not exceed the query index
-            if (ragged) hidden = hidden || (other0 + col >= prm.t_k);
-            if (hidden) s[e] = 0xff800000u;  // -inf: the probability becomes exactly 0
-          }
-        }
-        uint32_t p_packed[16], ds_packed[16];
+          for (int c = 0; c < 2; ++c)
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          uint64_t neg_l2, neg_delta;
-          if (kKV) {
-            const float2 a = *reinterpret_cast<const float2*>(st + c * 32 + e);
-            const float2 b = *reinterpret_cast<const float2*>(st + 64 + c * 32 + e);
-            neg_l2 = f2_pack(a.x, a.y);
-            neg_delta = f2_pack(b.x, b.y);
-          } else {
-            neg_l2 = row_neg_l2;
-            neg_delta = row_neg_delta;
-          }
-          float x0, x1;
-          f2_unpack(f2_fma(f2_pack_bits(s[e], s[e + 1]), sl2_2, neg_l2), x0, x1);
-          const float p0 = exp2_approx(x0), p1 = exp2_approx(x1);
-          float d0, d1;
-          f2_unpack(f2_mul(f2_pack(p0, p1), f2_add(f2_pack_bits(dp[e], dp[e + 1]), neg_delta)), d0, d1);
-          if (kKV) p_packed[e >> 1] = kFp16 ? pack_f16(p0, p1) : pack_bf16(p0, p1);
-          ds_packed[e >> 1] = kFp16 ? pack_f16(d0, d1) : pack_bf16(d0, d1);
+            for (int e = 0; e < 32; ++e) {
+              const int col = group * 64 + c * 32 + e;
+              bool hidden = false;
+              if (diagonal) hidden = kKV ? (col < r) : (col > r);   // a key index must not exceed the query index
+              if (ragged) hidden = hidden || (other0 + col >= prm.t_k);
+              if (hidden) s[c][e] = 0xff800000u;  // -inf: the probability becomes exactly 0
+            }
         }
-        if (kKV) tmem_st16(t_s + group * 64 + c * 16, p_packed);
-        tmem_st16(t_p + group * 64 + c * 16, ds_packed);
-        TRACE_EVENT(4 + c * 10);
+        uint32_t p_packed[32], ds_packed[32];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            uint64_t neg_l2, neg_delta;
+            if (kKV) {
+              const float2 a = *reinterpret_cast<const float2*>(st + c * 32 + e);
+              const float2 b = *reinterpret_cast<const float2*>(st + 64 + c * 32 + e);
+              neg_l2 = f2_pack(a.x, a.y);
+              neg_delta = f2_pack(b.x, b.y);
+            } else {
+              neg_l2 = row_neg_l2;
+              neg_delta = row_neg_delta;
+            }
+            float x0, x1;
+            f2_unpack(f2_fma(f2_pack_bits(s[c][e], s[c][e + 1]), sl2_2, neg_l2), x0, x1);
+            const float p0 = exp2_approx(x0), p1 = exp2_approx(x1);
+            float d0, d1;
+            f2_unpack(f2_mul(f2_pack(p0, p1), f2_add(f2_pack_bits(dp[c][e], dp[c][e + 1]), neg_delta)), d0, d1);
+            if (kKV) p_packed[c * 16 + (e >> 1)] = kFp16 ? pack_f16(p0, p1) : pack_bf16(p0, p1);
+            ds_packed[c * 16 + (e >> 1)] = kFp16 ? pack_f16(d0, d1) : pack_bf16(d0, d1);
+          }
+        }
+        TRACE_EVENT(4);
+        // the previous tile's products must have consumed the operand columns before they are rewritten
+        if (it > 0) {
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(B::ds_full + 1), (it - 1) & 1, prm.status, 0x1320u | group));
+          if (!ok) continue;
+          tc_fence_after_sync();
+        }
+        if (kKV) tmem_st32(tmem + lane_base + L::kPtCol + group * 32, p_packed);
+        tmem_st32(tmem + lane_base + L::kDsCol + group * 32, ds_packed);
+        tmem_st_wait();
+        TRACE_EVENT(5);
+        tc_fence_before_sync();
+        mbar_arrive(bar(B::ds_full));
+      } else {
+        TRACE_EVENT(1);
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full + group), it & 1, prm.status, 0x1300u | group));
+        if (!ok) continue;
+        TRACE_EVENT(2);
+        tc_fence_after_sync();
+        // which (lane, column) pairs take part: causal diagonal tile, and keys past t_k in the dQ pass
+        const bool diagonal = kCausal && other0 == own0;
+        const bool ragged = !kKV && other0 + kTile > prm.t_k;
+  #pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int col0 = group * 64 + c * 32;
+          uint32_t s[32], dp[32];
+          tmem_ld32(t_s + col0, s);
+          tmem_ld32(t_p + col0, dp);
+          tmem_ld_wait();
+          TRACE_EVENT(3 + c * 10);
+          if (diagonal || ragged) {
+  #pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              const int col = col0 + e;
+              bool hidden = false;
+              if (diagonal) hidden = kKV ? (col < r) : (col > r);   // a key index must not exceed the query index
+              if (ragged) hidden = hidden || (other0 + col >= prm.t_k);
+              if (hidden) s[e] = 0xff800000u;  // -inf: the probability becomes exactly 0
+            }
+          }
+          uint32_t p_packed[16], ds_packed[16];
+  #pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            uint64_t neg_l2, neg_delta;
+            if (kKV) {
+              const float2 a = *reinterpret_cast<const float2*>(st + c * 32 + e);
+              const float2 b = *reinterpret_cast<const float2*>(st + 64 + c * 32 + e);
+              neg_l2 = f2_pack(a.x, a.y);
+              neg_delta = f2_pack(b.x, b.y);
+            } else {
+              neg_l2 = row_neg_l2;
+              neg_delta = row_neg_delta;
+            }
+            float x0, x1;
+            f2_unpack(f2_fma(f2_pack_bits(s[e], s[e + 1]), sl2_2, neg_l2), x0, x1);
+            const float p0 = exp2_approx(x0), p1 = exp2_approx(x1);
+            float d0, d1;
+            f2_unpack(f2_mul(f2_pack(p0, p1), f2_add(f2_pack_bits(dp[e], dp[e + 1]), neg_delta)), d0, d1);
+            if (kKV) p_packed[e >> 1] = kFp16 ? pack_f16(p0, p1) : pack_bf16(p0, p1);
+            ds_packed[e >> 1] = kFp16 ? pack_f16(d0, d1) : pack_bf16(d0, d1);
+          }
+          if (kKV) tmem_st16(t_s + group * 64 + c * 16, p_packed);
+          tmem_st16(t_p + group * 64 + c * 16, ds_packed);
+          TRACE_EVENT(4 + c * 10);
+        }
+        tmem_st_wait();
+        TRACE_EVENT(5);
+        tc_fence_before_sync();
+        mbar_arrive(bar(B::ds_full + group));
       }
-      tmem_st_wait();
-      TRACE_EVENT(5);
-      tc_fence_before_sync();
-      mbar_arrive(bar(B::ds_full + group));
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::acc_full), 0, prm.status, 0x1310u));
     if (ok) {
@@ -429,7 +600,8 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
 template <int D, bool kCausal, bool kFp16, bool kKV>
 int launch_bwd(const Problem& p) {
-  using L = BwdLayout<D>;
+  constexpr bool kEarly = !kKV || D == 64;  // the dK/dV pass at head dim 128 has no spare tensor-memory columns
+  using L = BwdLayout<D, kKV>;
   CUtensorMap map_q, map_k, map_v, map_do;
   if (int rc = make_tile_map(&map_q, p.q, kFp16, p.bh, p.t_q, D, kTile)) return rc;
   if (int rc = make_tile_map(&map_k, p.k, kFp16, p.bh, p.t_k, D, kTile)) return rc;
@@ -452,7 +624,7 @@ int launch_bwd(const Problem& p) {
   prm.scale = static_cast<float>(p.scale);
   const long long ctas = p.bh * (kKV ? prm.kv_tiles : prm.q_tiles);
   if (ctas > 0x7fffffffLL) return fail(LIMN_B200_UNSUPPORTED, "sdpa backward: %lld CTAs exceed one grid", ctas);
-  auto kernel = sdpa_bwd_kernel<D, kCausal, kFp16, kKV>;
+  auto kernel = sdpa_bwd_kernel<D, kCausal, kFp16, kKV, kEarly>;
   LIMN_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes),
             "sizing shared memory for an sdpa backward kernel");
   kernel<<<dim3(static_cast<unsigned>(ctas)), dim3(kThreads), L::kBytes, p.stream>>>(map_q, map_k, map_v, map_do, prm);
