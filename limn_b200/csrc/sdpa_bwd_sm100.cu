@@ -412,20 +412,24 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       row_neg_l2 = f2_pack(nl, nl);
       row_neg_delta = f2_pack(nd, nd);
     }
+    // dK/dV pass: one per-query statistic per thread per streamed tile (-L log2e for the first 64 threads of a
+    // group, -delta for the rest), read from global memory one tile ahead of its use
+    auto fetch_stat = [&](int tile0) {
+      const int query = tile0 + group * 64 + (r & 63);
+      const bool in = query < prm.t_q;
+      if ((r >> 6) == 0) return in ? -prm.lse[stat_base + query] * kLog2e : -INFINITY;
+      return in ? -prm.delta[stat_base + query] : 0.f;
+    };
+    float fetched = kKV ? fetch_stat(first * kTile) : 0.f;
     for (int it = 0; it < count; ++it) {
       const int other0 = (first + it) * kTile;  // first key (dQ pass) or first query (dK/dV pass) of the streamed tile
       // per group: [2 buffers][-L log2e, -delta][64 columns]
       float* st = stat + group * (2 * 2 * 64) + (it & 1) * (2 * 64);
       if (kKV) {
-        // per-query statistics of this group's 64 columns -> shared memory, one value per thread
-        const int which = r >> 6, idx = r & 63;
-        const int query = other0 + group * 64 + idx;
-        const bool in = query < prm.t_q;
-        float val;
-        if (which == 0) val = in ? -prm.lse[stat_base + query] * kLog2e : -INFINITY;
-        else val = in ? -prm.delta[stat_base + query] : 0.f;
-        st[which * 64 + idx] = val;
+        // this tile's statistics were fetched while the previous tile was being worked on
+        st[(r >> 6) * 64 + (r & 63)] = fetched;
         group_barrier(group);  // every thread of the group reaches this every iteration, whatever `ok` is
+        if (it + 1 < count) fetched = fetch_stat(other0 + kTile);
       }
       if constexpr (kEarly) {
         TRACE_EVENT(1);

@@ -13,6 +13,8 @@
 #include <cuda_fp16.h>
 
 #include <cmath>
+#include <cstdint>
+#include <type_traits>
 
 #include "common.h"
 
@@ -278,6 +280,64 @@ row_dot_kernel(const T* __restrict__ out, const T* __restrict__ dout, C* __restr
   if (lane == 0) delta[row] = acc;
 }
 
+
+// The same row dot for 2-byte storage when a row is a whole number of 16-byte pieces: each
+// thread takes 8 elements of one row with one 16-byte load from each tensor, and the
+// threads of a row (hd_v / 8 of them, a power of two up to 32, consecutive lanes) fold their
+// partial sums with shuffles. Both tensors are read exactly once at full sector width, so the
+// kernel runs at memory speed; the generic kernel above serves every other shape.
+template <bool kFp16, int kLanes>
+__global__ void __launch_bounds__(256)
+row_dot16_kernel(const uint4* __restrict__ out, const uint4* __restrict__ dout, float* __restrict__ delta,
+                 long long rows) {
+  const long long piece = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;  // 16-byte piece index
+  const long long row = piece / kLanes;
+  float acc = 0.f;
+  if (row < rows) {
+    const uint4 a = out[piece], b = dout[piece];
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float a0, a1, b0, b1;
+      if (kFp16) {
+        const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&aw[i]));
+        const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&bw[i]));
+        a0 = fa.x, a1 = fa.y, b0 = fb.x, b1 = fb.y;
+      } else {
+        a0 = __uint_as_float(aw[i] << 16), a1 = __uint_as_float(aw[i] & 0xffff0000u);
+        b0 = __uint_as_float(bw[i] << 16), b1 = __uint_as_float(bw[i] & 0xffff0000u);
+      }
+      acc = fmaf(a0, b0, acc);
+      acc = fmaf(a1, b1, acc);
+    }
+  }
+#pragma unroll
+  for (int off = kLanes / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(kFull, acc, off);
+  if (row < rows && (threadIdx.x & (kLanes - 1)) == 0) delta[row] = acc;
+}
+
+template <bool kFp16>
+bool launch_row_dot16(const void* out, const void* dout, void* delta, long long rows, int hd_v, cudaStream_t stream) {
+  const int lanes = hd_v / 8;
+  if (hd_v % 8 != 0 || lanes > 32 || (lanes & (lanes - 1)) != 0) return false;
+  if ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(dout)) & 15u) return false;
+  const long long pieces = rows * lanes;
+  const long long blocks = (pieces + 255) / 256;
+  if (blocks > 0x7fffffffLL) return false;
+  const dim3 grid(static_cast<unsigned>(blocks)), block(256);
+  auto a = static_cast<const uint4*>(out), b = static_cast<const uint4*>(dout);
+  auto d = static_cast<float*>(delta);
+  switch (lanes) {
+    case 1: row_dot16_kernel<kFp16, 1><<<grid, block, 0, stream>>>(a, b, d, rows); break;
+    case 2: row_dot16_kernel<kFp16, 2><<<grid, block, 0, stream>>>(a, b, d, rows); break;
+    case 4: row_dot16_kernel<kFp16, 4><<<grid, block, 0, stream>>>(a, b, d, rows); break;
+    case 8: row_dot16_kernel<kFp16, 8><<<grid, block, 0, stream>>>(a, b, d, rows); break;
+    case 16: row_dot16_kernel<kFp16, 16><<<grid, block, 0, stream>>>(a, b, d, rows); break;
+    default: row_dot16_kernel<kFp16, 32><<<grid, block, 0, stream>>>(a, b, d, rows); break;
+  }
+  return true;
+}
+
 template <typename T, typename C, int ND>
 int launch_typed(Op op, const Problem& p) {
   const long long rows = p.bh * (op == Op::BwdKV ? p.t_k : p.t_q);
@@ -349,6 +409,12 @@ int general_delta(const void* out, const void* dout, void* delta, int dtype, lon
   const long long blocks = (rows + kWarps - 1) / kWarps;
   if (blocks > 0x7fffffffLL) return fail(LIMN_B200_UNSUPPORTED, "sdpa_delta: %lld rows need more blocks than one grid holds", rows);
   const dim3 grid(static_cast<unsigned>(blocks)), block(kWarps * 32);
+  if ((dtype == LIMN_B200_F16 && launch_row_dot16<true>(out, dout, delta, rows, hd_v, stream)) ||
+      (dtype == LIMN_B200_BF16 && launch_row_dot16<false>(out, dout, delta, rows, hd_v, stream))) {
+    LIMN_CUDA(cudaGetLastError(), "launching the row-dot kernel");
+    note_launches(1);
+    return LIMN_B200_OK;
+  }
   switch (dtype) {
     case LIMN_B200_F32:
       row_dot_kernel<float, float><<<grid, block, 0, stream>>>((const float*)out, (const float*)dout, (float*)delta, rows, hd_v);
