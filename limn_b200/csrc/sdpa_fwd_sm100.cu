@@ -18,6 +18,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "common.h"
 #include "sm100_ptx.cuh"
 #include "tensor_map.h"
@@ -70,7 +72,18 @@ struct FwdBars {
   static constexpr int count = o_full + 2;
 };
 
+// Build-time diagnostic (-DLIMN_TRACE): one CTA records clock64() at each step of its pipeline into a
+// buffer named by the LIMN_TRACE_PTR environment variable. Compiled out of the shipped library.
+#ifdef LIMN_TRACE
+#define TRACE_EVENT(code) do { if (blockIdx.x == 7 && lane == 0 && trace_n < 250) { prm.trace[warp * 512 + 2 * trace_n] = clock64(); prm.trace[warp * 512 + 2 * trace_n + 1] = (code); ++trace_n; } } while (0)
+#else
+#define TRACE_EVENT(code) do {} while (0)
+#endif
+
 struct FwdParams {
+#ifdef LIMN_TRACE
+  long long* trace;
+#endif
   void* out;
   float* lse;
   unsigned* status;
@@ -133,6 +146,10 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t tmem = tmem_slot;
 
   bool ok = true;
+#ifdef LIMN_TRACE
+  int trace_n = 0;
+#endif
+  TRACE_EVENT(0);
 
   if (warp == kProducerWarp) {
     // ================= TMA producer =================
@@ -221,16 +238,20 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
         for (int t = 0; t < kQTiles; ++t) {
           if (!ok || j >= n_kv[t]) continue;
+          TRACE_EVENT(100 + t);
           ok = mbar_wait(bar(B::p_full + t), j & 1, prm.status, 0x0230u | t);
           if (!ok) break;
+          TRACE_EVENT(110 + t);
           tc_fence_after_sync();
           issue_pv(t, stage, j == 0);
+          TRACE_EVENT(120 + t);
           if (j + 1 < n_kv[t]) {
             ok = mbar_wait(bar(B::k_full + next), next_wrap, prm.status, 0x0240u | next);
             if (!ok) break;
             tc_fence_after_sync();
             issue_s(t, next);
-            mma_commit(bar(B::s_full + t));  // also covers the PV above: O_t is settled when S_t is ready
+            mma_commit(bar(B::s_full + t));
+            TRACE_EVENT(130 + t);  // also covers the PV above: O_t is settled when S_t is ready
             issued_next = true;
           } else {
             mma_commit(bar(B::o_full + t));
@@ -260,11 +281,13 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     for (int j = 0; j < n; ++j) {
       ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full + t), j & 1, prm.status, 0x0300u | t));  // warp-uniform: the tensor-memory ops below are warp-wide
       if (!ok) break;
+      TRACE_EVENT(2);
       tc_fence_after_sync();
       uint32_t s[4][32];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(t_s + 32 * c, s[c]);
       tmem_ld_wait();
+      TRACE_EVENT(3);
       const int kv0 = j * kTileRows;
       const bool diagonal = kCausal && kv0 + kTileRows > q0[t];     // some key of this tile is right of some row
       const bool ragged = kv0 + kTileRows > prm.t_k;                // some key of this tile does not exist
@@ -290,6 +313,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         alpha = exp2_approx((m - mx) * sl2);
         m = mx;
       }
+      TRACE_EVENT(4);
       const float shift = -m * sl2;
       const uint64_t shift2 = f2_pack(shift, shift);
       uint64_t sum2[2] = {0ull, 0ull};
@@ -316,6 +340,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
         tmem_st32(t_s + 32 * h, packed);
       }
+      TRACE_EVENT(5);
       float sum_a, sum_b, sum_c, sum_d;
       f2_unpack(sum2[0], sum_a, sum_b);
       f2_unpack(sum2[1], sum_c, sum_d);
@@ -333,6 +358,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
       }
       tmem_st_wait();
+      TRACE_EVENT(6);
       tc_fence_before_sync();
       mbar_arrive(bar(B::p_full + t));
     }
@@ -395,6 +421,9 @@ int launch_fwd(const Problem& p) {
   prm.t_q = p.t_q, prm.t_k = p.t_k;
   prm.q_pairs = (p.t_q + kQTiles * kTileRows - 1) / (kQTiles * kTileRows);
   prm.kv_tiles = (p.t_k + kTileRows - 1) / kTileRows;
+#ifdef LIMN_TRACE
+  prm.trace = reinterpret_cast<long long*>(strtoull(getenv("LIMN_TRACE_PTR"), nullptr, 16));
+#endif
   prm.scale = static_cast<float>(p.scale);
   const long long ctas = p.bh * prm.q_pairs;
   if (ctas > 0x7fffffffLL) return fail(LIMN_B200_UNSUPPORTED, "sdpa: %lld CTAs exceed one grid", ctas);
