@@ -100,7 +100,7 @@ __device__ __forceinline__ void tc_fence_after_sync() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
-// ---- TMA: 3-D tiled load global -> shared, completion on an mbarrier (no multicast) ----
+// ---- TMA: 3-D tiled load global -> shared, completion on an mbarrier; every CTA fetches its own tiles ----
 __device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
