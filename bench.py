@@ -348,6 +348,7 @@ def gpu_arm(args) -> None:
     runtime.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
+        os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout: rank 0 prints exactly one line
         dist.init_process_group("nccl", device_id=device)
 
     def barrier() -> None:
@@ -455,7 +456,7 @@ def gpu_arm(args) -> None:
                              "sample": f"{sample} of {bh} (batch, head) problems, {cpu_seconds:.1f} s"},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": up * world, "d2h_bytes_per_step": down * world,
                     "ms_per_step": e2e_ms / e2e_steps},
-            "gpu_launches": launches,
+            "gpu_launches": launches * world,
             "clocks": clocks,
             "gather_ms": gather_ms,
             "parity": parity,

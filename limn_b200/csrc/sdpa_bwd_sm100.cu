@@ -53,7 +53,7 @@ struct BwdLayout {
   static constexpr int kStreamAOff = 2 * kTileBytes;               // ring of the first streamed tile (K, or Q)
   static constexpr int kStreamBOff = kStreamAOff + kStagesA * kTileBytes;  // ring of the second (V, or dO)
   static constexpr int kStatOff = kStreamBOff + kStagesB * kTileBytes;
-  static constexpr int kBarOff = kStatOff + (kKV ? 2 * 2 * kTile * 4 : 0);  // statistics (dK/dV pass only): [2 groups][2 buffers][-L, -delta][64]
+  static constexpr int kBarOff = kStatOff + (kKV ? 8 * 2 * 2 * 64 * 4 : 0);  // statistics (dK/dV pass only): [8 warps][2 buffers][-L, -delta][64]
   static constexpr int kBytes = kBarOff + 256 + 1024;
   static_assert(kBytes <= 227 * 1024, "shared memory per CTA");
   // tensor-memory columns
@@ -412,23 +412,29 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       row_neg_l2 = f2_pack(nl, nl);
       row_neg_delta = f2_pack(nd, nd);
     }
-    // dK/dV pass: one per-query statistic per thread per streamed tile (-L log2e for the first 64 threads of a
-    // group, -delta for the rest), read from global memory one tile ahead of its use
+    // dK/dV pass: the statistics of the streamed tile's queries. Every warp keeps its own copy of its group's
+    // 64 columns in shared memory (-L log2e then -delta), each lane fetching two columns of each from global
+    // memory one tile ahead of their use, so no warp ever waits for another here.
+    struct Fetched { float l0, l1, d0, d1; };
     auto fetch_stat = [&](int tile0) {
-      const int query = tile0 + group * 64 + (r & 63);
-      const bool in = query < prm.t_q;
-      if ((r >> 6) == 0) return in ? -prm.lse[stat_base + query] * kLog2e : -INFINITY;
-      return in ? -prm.delta[stat_base + query] : 0.f;
+      Fetched f;
+      const int q0 = tile0 + group * 64 + lane, q1 = q0 + 32;
+      f.l0 = q0 < prm.t_q ? -prm.lse[stat_base + q0] * kLog2e : -INFINITY;
+      f.l1 = q1 < prm.t_q ? -prm.lse[stat_base + q1] * kLog2e : -INFINITY;
+      f.d0 = q0 < prm.t_q ? -prm.delta[stat_base + q0] : 0.f;
+      f.d1 = q1 < prm.t_q ? -prm.delta[stat_base + q1] : 0.f;
+      return f;
     };
-    float fetched = kKV ? fetch_stat(first * kTile) : 0.f;
+    Fetched fetched = {0.f, 0.f, 0.f, 0.f};
+    if (kKV) fetched = fetch_stat(first * kTile);
     for (int it = 0; it < count; ++it) {
       const int other0 = (first + it) * kTile;  // first key (dQ pass) or first query (dK/dV pass) of the streamed tile
-      // per group: [2 buffers][-L log2e, -delta][64 columns]
-      float* st = stat + group * (2 * 2 * 64) + (it & 1) * (2 * 64);
+      // per warp: [2 buffers][-L log2e, -delta][64 columns]
+      float* st = stat + (warp * 2 + (it & 1)) * (2 * 64);
       if (kKV) {
-        // this tile's statistics were fetched while the previous tile was being worked on
-        st[(r >> 6) * 64 + (r & 63)] = fetched;
-        group_barrier(group);  // every thread of the group reaches this every iteration, whatever `ok` is
+        st[lane] = fetched.l0, st[lane + 32] = fetched.l1;
+        st[64 + lane] = fetched.d0, st[96 + lane] = fetched.d1;
+        __syncwarp();
         if (it + 1 < count) fetched = fetch_stat(other0 + kTile);
       }
       if constexpr (kEarly) {
