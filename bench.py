@@ -97,6 +97,14 @@ def reduce_max(value: float, dist, device) -> float:
     return float(t.item())
 
 
+def forward_traffic(workload: str, problems: int):
+    """DRAM bytes (read + write) of one forward launch, from the ncu captures summarised under profiles/:
+    measured on a subset of the workload's problems and scaled by the problem count, to which it is
+    proportional (every problem's tensors cross HBM once). None where no capture exists."""
+    per_problem = {"prefill_4k": (201.563904e6 + 50.116864e6) / 64, "encoder_2k": (100.886272e6 + 17.199872e6) / 128}
+    return per_problem[workload] * problems if workload in per_problem else None
+
+
 def peaks() -> tuple[dict, str]:
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
@@ -222,12 +230,13 @@ def reference_arm(args) -> None:
 class Shard:
     """One rank's problems of a workload, resident on its GPU as torch tensors."""
 
-    def __init__(self, workload: str, first: int, count: int, torch, device):
+    def __init__(self, workload: str, first: int, count: int, torch, device, force_backward: bool = False):
         from limn_b200._lib import lib
 
         self.lib = lib()
         self.workload = workload
         b, h, s, d, causal, backward, *_ = WORKLOADS[workload]
+        backward = backward or force_backward
         self.count, self.s, self.d, self.causal, self.backward = count, s, d, causal, backward
         self.scale = d ** -0.5
         host = shard_inputs(workload, first, count, backward)
@@ -451,7 +460,7 @@ def gpu_arm(args) -> None:
                             "of_nominal_2250": 100 * value / world / 2250.0},
             "roofline": {"bound": "tensor", "kernel": "sdpa_fwd_kernel", "achieved": fwd_rate, "peak": tensor_peak, "unit": "TFLOP/s",
                          "frac": fwd_rate / tensor_peak, "peak_kind": f"{peak_kind} burst (kernel timed alone, {args.steps} launches)",
-                         "traffic": None, "ms_per_launch": fwd_ms},
+                         "traffic": forward_traffic(workload, per_rank), "ms_per_launch": fwd_ms},
             "cpu_baseline": {"value": cpu_flops / cpu_seconds / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count() or 1, "kind": "port",
                              "sample": f"{sample} of {bh} (batch, head) problems, {cpu_seconds:.1f} s"},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": up * world, "d2h_bytes_per_step": down * world,
@@ -467,6 +476,27 @@ def gpu_arm(args) -> None:
         dist.destroy_process_group()
 
 
+def profile_case(args) -> None:
+    """For profiler captures: the first N problems of a workload, each kernel of the path launched
+    `--steps` times after one warm-up pass, nothing timed and nothing printed but a status line.
+    `ncu -k regex:sdpa_ ...  python bench.py --profile N --workload W [--backward]` then sees a small,
+    bounded case of the same kernels on the same seeded inputs."""
+    import torch
+
+    from limn_b200 import runtime
+
+    torch.cuda.set_device(0)
+    runtime.set_device(0)
+    b, h, s, d, causal, backward, *_ = WORKLOADS[args.workload]
+    count = min(args.profile, b * h)
+    shard = Shard(args.workload, 0, count, torch, torch.device("cuda", 0), force_backward=args.backward)
+    shard.step()
+    for _ in range(args.steps):
+        shard.step()
+    torch.cuda.synchronize()
+    print(json.dumps({"profiled": args.workload, "problems": count, "backward": shard.backward, "device_status": runtime.device_status()}))
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -474,9 +504,13 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", choices=("limn_b200", "reference"), default="limn_b200")
     parser.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT_WORKLOAD)
+    parser.add_argument("--profile", type=int, default=0, metavar="N", help="launch the kernels over the first N problems and exit (for ncu)")
+    parser.add_argument("--backward", action="store_true", help="with --profile: run the backward kernels even for a forward-only workload")
     parser.add_argument("--no-others", dest="others", action="store_false", help="time only the named workload")
     args = parser.parse_args()
-    if args.impl == "reference":
+    if args.profile:
+        profile_case(args)
+    elif args.impl == "reference":
         reference_arm(args)
     else:
         gpu_arm(args)
