@@ -69,7 +69,8 @@ struct FwdBars {
   static constexpr int s_full = v_empty + kS;    // + t
   static constexpr int p_full = s_full + 2;      // + t
   static constexpr int o_full = p_full + 2;      // + t
-  static constexpr int count = o_full + 2;
+  static constexpr int p_half = o_full + 2;      // + t: the first 64 keys' worth of P_t is in place (and O_t rescaled)
+  static constexpr int count = p_half + 2;
 };
 
 // Build-time diagnostic (-DLIMN_TRACE): one CTA records clock64() at each step of its pipeline into a
@@ -129,7 +130,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (threadIdx.x == 0) {
     abort_flag = *reinterpret_cast<volatile unsigned*>(prm.status) != kStatusOk;
     for (int i = 0; i < B::count; ++i) {
-      const bool softmax_arrives = i >= B::p_full && i < B::p_full + 2;
+      const bool softmax_arrives = (i >= B::p_full && i < B::p_full + 2) || (i >= B::p_half && i < B::p_half + 2);
       mbar_init(bar(i), softmax_arrives ? 128u : 1u);
     }
     mbar_init_fence();
@@ -204,12 +205,12 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
       };
       // O_t += P_t V over the 128 keys of the tile, 16 keys per instruction
-      auto issue_pv = [&](int t, int stage, bool first) {
+      auto issue_pv = [&](int t, int stage, int part, bool first) {
         const uint32_t v_lo = desc_lo(base + L::kVOff + stage * L::kTileBytes, L::kAtomBytes);
         const uint32_t c = tmem + L::kOCol + t * D;
         const uint32_t a = tmem + L::kSCol + t * 128;
 #pragma unroll
-        for (int kk = 0; kk < kTileRows / 16; ++kk)
+        for (int kk = 4 * part; kk < 4 * part + 4; ++kk)
           mma_ts_lo(c, a + kk * 8, v_lo + kk * (16 * 128 / 16), idesc_pv, (kk > 0 || !first) ? 1u : 0u);
       };
 #pragma unroll
@@ -239,11 +240,16 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         for (int t = 0; t < kQTiles; ++t) {
           if (!ok || j >= n_kv[t]) continue;
           TRACE_EVENT(100 + t);
+          // the product starts on the first 64 keys while the softmax is still on the last 64
+          ok = mbar_wait(bar(B::p_half + t), j & 1, prm.status, 0x0260u | t);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_pv(t, stage, 0, j == 0);
           ok = mbar_wait(bar(B::p_full + t), j & 1, prm.status, 0x0230u | t);
           if (!ok) break;
           TRACE_EVENT(110 + t);
           tc_fence_after_sync();
-          issue_pv(t, stage, j == 0);
+          issue_pv(t, stage, 1, j == 0);
           TRACE_EVENT(120 + t);
           if (j + 1 < n_kv[t]) {
             ok = mbar_wait(bar(B::k_full + next), next_wrap, prm.status, 0x0240u | next);
@@ -319,6 +325,22 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
+        if (h == 1) {
+        // O_t was last written by the PV of tile j-1, which s_full also covers. It is rescaled before any of
+        // this tile's P_t is handed over (the product on the first half starts early), at the point where
+        // the first half's scores are no longer held in registers.
+        if (j > 0 && __any_sync(0xffffffffu, moves)) {
+  #pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(t_o + 32 * c, o);
+            tmem_ld_wait();
+  #pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(t_o + 32 * c, o);
+          }
+        }
+        }
         uint32_t packed[32];
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
@@ -337,6 +359,12 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             sum2[(i >> 1) & 1] = f2_add(sum2[(i >> 1) & 1], f2_pack(p0, p1));
             packed[cc * 16 + (i >> 1)] = kFp16 ? pack_f16(p0, p1) : pack_bf16(p0, p1);
           }
+          if (h == 1 && cc == 0) {
+            // the first half's store was issued a chunk of exponentials ago; hand it over
+            tmem_st_wait();
+            tc_fence_before_sync();
+            mbar_arrive(bar(B::p_half + t));
+          }
         }
         tmem_st32(t_s + 32 * h, packed);
       }
@@ -345,18 +373,6 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       f2_unpack(sum2[0], sum_a, sum_b);
       f2_unpack(sum2[1], sum_c, sum_d);
       l = l * alpha + ((sum_a + sum_b) + (sum_c + sum_d));
-      // O_t was last written by the PV of tile j-1, which s_full also covers
-      if (j > 0 && __any_sync(0xffffffffu, moves)) {
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t o[32];
-          tmem_ld32(t_o + 32 * c, o);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st32(t_o + 32 * c, o);
-        }
-      }
       tmem_st_wait();
       TRACE_EVENT(6);
       tc_fence_before_sync();
