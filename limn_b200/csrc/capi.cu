@@ -70,6 +70,25 @@ int make_tile_map(CUtensorMap* map, const void* base, bool fp16, long long bh, i
     return fail(LIMN_B200_CUDA_ERROR, "cuda: the driver does not export cuTensorMapEncodeTiled");
   if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0)
     return fail(LIMN_B200_BAD_ARGUMENT, "sdpa: tensor base %p is not 16-byte aligned", base);
+  // A map depends only on the base address and the extents, and a host that pools its buffers (limn does,
+  // limn/backend_cuda.py:297-307) hands the same ones back step after step, so the last few encodings are kept
+  // per thread. At the smallest shapes the encoding costs as much host time as the kernel takes to run.
+  struct Entry {
+    const void* base;
+    long long bh;
+    int rows, width, box_rows, fp16;
+    CUtensorMap map;
+  };
+  constexpr int kEntries = 16;
+  thread_local Entry cache[kEntries];
+  thread_local int used = 0, next_slot = 0;
+  for (int i = 0; i < used; ++i) {
+    const Entry& e = cache[i];
+    if (e.base == base && e.bh == bh && e.rows == rows && e.width == width && e.box_rows == box_rows && e.fp16 == (fp16 ? 1 : 0)) {
+      *map = e.map;
+      return LIMN_B200_OK;
+    }
+  }
   const cuuint64_t dims[3] = {static_cast<cuuint64_t>(width), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(bh)};
   const cuuint64_t strides[2] = {static_cast<cuuint64_t>(width) * 2, static_cast<cuuint64_t>(rows) * width * 2};
   const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
@@ -79,6 +98,10 @@ int make_tile_map(CUtensorMap* map, const void* base, bool fp16, long long bh, i
       strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (res != CUDA_SUCCESS) return fail(LIMN_B200_CUDA_ERROR, "cuda: encoding a tensor map failed with CUresult %d", (int)res);
+  Entry& slot = cache[next_slot];
+  slot = Entry{base, bh, rows, width, box_rows, fp16 ? 1 : 0, *map};
+  next_slot = (next_slot + 1) % kEntries;
+  if (used < kEntries) ++used;
   return LIMN_B200_OK;
 }
 

@@ -647,8 +647,15 @@ int launch_bwd(const Problem& p) {
   const long long ctas = p.bh * (kKV ? prm.kv_tiles : prm.q_tiles);
   if (ctas > 0x7fffffffLL) return fail(LIMN_B200_UNSUPPORTED, "sdpa backward: %lld CTAs exceed one grid", ctas);
   auto kernel = sdpa_bwd_kernel<D, kCausal, kFp16, kKV, kEarly>;
-  LIMN_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes),
-            "sizing shared memory for an sdpa backward kernel");
+  // the attribute is per device and per kernel instantiation; set it on first use there
+  static bool sized[64] = {};
+  int device = 0;
+  LIMN_CUDA(cudaGetDevice(&device), "asking for the current device");
+  if (device >= 0 && device < 64 && !sized[device]) {
+    LIMN_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes),
+              "sizing shared memory for an sdpa backward kernel");
+    sized[device] = true;
+  }
   kernel<<<dim3(static_cast<unsigned>(ctas)), dim3(kThreads), L::kBytes, p.stream>>>(map_q, map_k, map_v, map_do, prm);
   LIMN_CUDA(cudaGetLastError(), "launching an sdpa backward kernel");
   note_launches(1);

@@ -444,11 +444,14 @@ int launch_fwd(const Problem& p) {
   const long long ctas = p.bh * prm.q_pairs;
   if (ctas > 0x7fffffffLL) return fail(LIMN_B200_UNSUPPORTED, "sdpa: %lld CTAs exceed one grid", ctas);
   auto kernel = sdpa_fwd_kernel<D, kCausal, kFp16>;
-  static bool sized = false;  // per instantiation
-  if (!sized) {
+  // the attribute is per device and per kernel instantiation; set it on first use there
+  static bool sized[64] = {};
+  int device = 0;
+  LIMN_CUDA(cudaGetDevice(&device), "asking for the current device");
+  if (device >= 0 && device < 64 && !sized[device]) {
     LIMN_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes),
               "sizing shared memory for the sdpa kernel");
-    sized = true;
+    sized[device] = true;
   }
   kernel<<<dim3(static_cast<unsigned>(ctas)), dim3(kThreads), L::kBytes, p.stream>>>(map_q, map_k, map_v, prm);
   LIMN_CUDA(cudaGetLastError(), "launching the sdpa kernel");
