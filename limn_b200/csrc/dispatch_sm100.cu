@@ -10,7 +10,6 @@ int tcgen05_bwd_kv(const Problem& p);
 bool tcgen05_serves(Op op, const Problem& p) {
   if (p.dtype != LIMN_B200_BF16 && p.dtype != LIMN_B200_F16) return false;
   if (p.hd != p.hd_v || (p.hd != 64 && p.hd != 128)) return false;
-  if (p.mask != nullptr) return false;
   if (!(p.scale > 0.0)) return false;          // the softmax folds the scale into exp2 and takes row maxima before scaling
   if (p.bh > 0x7fffffffLL) return false;       // problem index is a 32-bit TMA coordinate
   return true;

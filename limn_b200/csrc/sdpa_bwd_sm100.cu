@@ -48,19 +48,19 @@ constexpr float kLog2e = 1.4426950408889634f;
 #endif
 constexpr int kPolyPairsOf8 = LIMN_BWD_POLY_PAIRS;
 
-template <int D, bool kKV>
+template <int D, bool kKV, bool kMask>
 struct BwdLayout {
   static constexpr int kTileBytes = kTile * D * 2;
   static constexpr int kAtomBytes = kTile * 128;
   // ring depths of the two streamed tiles. In the dQ pass at head dim 128 the V tile is only read by the
   // scores and leaves early, so two slots do for it and K gets the third that shared memory has room for.
-  static constexpr int kStagesA = D == 128 ? (kKV ? 2 : 3) : 3;
+  static constexpr int kStagesA = D == 128 ? ((kKV || kMask) ? 2 : 3) : 3;  // a key mask's staging takes the room of the third slot
   static constexpr int kStagesB = D == 128 ? 2 : 3;
   static constexpr int kHeldOff = 0;                               // two resident tiles
   static constexpr int kStreamAOff = 2 * kTileBytes;               // ring of the first streamed tile (K, or Q)
   static constexpr int kStreamBOff = kStreamAOff + kStagesA * kTileBytes;  // ring of the second (V, or dO)
   static constexpr int kStatOff = kStreamBOff + kStagesB * kTileBytes;
-  static constexpr int kBarOff = kStatOff + (kKV ? 8 * 2 * 2 * 64 * 4 : 0);  // statistics (dK/dV pass only): [8 warps][2 buffers][-L, -delta][64]
+  static constexpr int kBarOff = kStatOff + ((kKV || kMask) ? 8 * 2 * 2 * 64 * 4 : 0);  // per warp [2 buffers][128 floats]: statistics (dK/dV pass) or key-mask bias (dQ pass)
   static constexpr int kBytes = kBarOff + 256 + 1024;
   static_assert(kBytes <= 227 * 1024, "shared memory per CTA");
   // tensor-memory columns
@@ -72,9 +72,9 @@ struct BwdLayout {
   static constexpr int kPtCol = 384;     // early schedule, dK/dV pass at head dim 64: P^T as 16-bit, 64 columns
 };
 
-template <int D, bool kKV>
+template <int D, bool kKV, bool kMask>
 struct BwdBars {
-  static constexpr int kSA = BwdLayout<D, kKV>::kStagesA, kSB = BwdLayout<D, kKV>::kStagesB;
+  static constexpr int kSA = BwdLayout<D, kKV, kMask>::kStagesA, kSB = BwdLayout<D, kKV, kMask>::kStagesB;
   static constexpr int held_full = 0;
   static constexpr int a_full = 1;                // + slot
   static constexpr int a_empty = a_full + kSA;
@@ -98,6 +98,7 @@ struct BwdParams {
 #ifdef LIMN_TRACE
   long long* trace;
 #endif
+  const unsigned short* mask;  // (bh, t_k) key flags in the storage dtype, 0 hides a key; null without a mask
   const float* lse;
   const float* delta;
   void* out0;   // dQ, or dK
@@ -134,13 +135,13 @@ __device__ __forceinline__ void store_row32(void* base, long long elem_offset, c
 // run beside the elementwise stage; it needs 64 (dQ pass) or 128 (dK/dV pass) spare columns, which the
 // dK/dV pass has only at head dim 64. false: the operands overlay the scores and the tile is pipelined in
 // two 64-column halves instead.
-template <int D, bool kCausal, bool kFp16, bool kKV, bool kEarly>
+template <int D, bool kCausal, bool kFp16, bool kKV, bool kEarly, bool kMask>
 __global__ void __launch_bounds__(kThreads, 1)
 sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                 const BwdParams prm) {
-  using L = BwdLayout<D, kKV>;
-  using B = BwdBars<D, kKV>;
+  using L = BwdLayout<D, kKV, kMask>;
+  using B = BwdBars<D, kKV, kMask>;
   extern __shared__ unsigned char smem_unaligned[];
   __shared__ uint32_t tmem_slot;
   __shared__ uint32_t abort_flag;
@@ -434,10 +435,36 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     };
     Fetched fetched = {0.f, 0.f, 0.f, 0.f};
     if (kKV) fetched = fetch_stat(first * kTile);
+    // Key mask: a hidden key's probabilities are exactly 0, which an additive -inf on its scores gives. In the
+    // dK/dV pass the key is this thread's own row, one flag for the whole pass; in the dQ pass keys are the
+    // columns, and each warp stages its group's 64 flags per streamed tile, fetched one tile ahead.
+    auto key_bias = [&](int key) {
+      const bool live = key < prm.t_k && (prm.mask[static_cast<long long>(problem) * prm.t_k + key] & 0x7fffu) != 0;
+      return live ? 0.f : -INFINITY;
+    };
+    uint64_t row_bias2 = 0;
+    float col_bias0 = 0.f, col_bias1 = 0.f;
+    if (kMask) {
+      if (kKV) {
+        const float b = key_bias(own0 + r);
+        row_bias2 = f2_pack(b, b);
+      } else {
+        col_bias0 = key_bias(first * kTile + group * 64 + lane);
+        col_bias1 = key_bias(first * kTile + group * 64 + lane + 32);
+      }
+    }
     for (int it = 0; it < count; ++it) {
       const int other0 = (first + it) * kTile;  // first key (dQ pass) or first query (dK/dV pass) of the streamed tile
       // per warp: [2 buffers][-L log2e, -delta][64 columns]
       float* st = stat + (warp * 2 + (it & 1)) * (2 * 64);
+      if (kMask && !kKV) {
+        st[lane] = col_bias0, st[lane + 32] = col_bias1;
+        __syncwarp();
+        if (it + 1 < count) {
+          col_bias0 = key_bias(other0 + kTile + group * 64 + lane);
+          col_bias1 = key_bias(other0 + kTile + group * 64 + lane + 32);
+        }
+      }
       if (kKV) {
         st[lane] = fetched.l0, st[lane + 32] = fetched.l1;
         st[64 + lane] = fetched.d0, st[96 + lane] = fetched.d1;
@@ -488,6 +515,14 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             } else {
               neg_l2 = row_neg_l2;
               neg_delta = row_neg_delta;
+            }
+            if (kMask) {
+              if (kKV) {
+                neg_l2 = f2_add(neg_l2, row_bias2);
+              } else {
+                const float2 b = *reinterpret_cast<const float2*>(st + c * 32 + e);
+                neg_l2 = f2_add(neg_l2, f2_pack(b.x, b.y));
+              }
             }
             const uint64_t x2 = f2_fma(f2_pack_bits(s[c][e], s[c][e + 1]), sl2_2, neg_l2);
             float p0, p1;
@@ -557,6 +592,14 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
               neg_delta = row_neg_delta;
             }
             float x0, x1;
+            if (kMask) {
+              if (kKV) {
+                neg_l2 = f2_add(neg_l2, row_bias2);
+              } else {
+                const float2 b = *reinterpret_cast<const float2*>(st + c * 32 + e);
+                neg_l2 = f2_add(neg_l2, f2_pack(b.x, b.y));
+              }
+            }
             f2_unpack(f2_fma(f2_pack_bits(s[e], s[e + 1]), sl2_2, neg_l2), x0, x1);
             const float p0 = exp2_approx(x0), p1 = exp2_approx(x1);
             float d0, d1;
@@ -620,16 +663,17 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   }
 }
 
-template <int D, bool kCausal, bool kFp16, bool kKV>
+template <int D, bool kCausal, bool kFp16, bool kKV, bool kMask>
 int launch_bwd(const Problem& p) {
   constexpr bool kEarly = !kKV || D == 64;  // the dK/dV pass at head dim 128 has no spare tensor-memory columns
-  using L = BwdLayout<D, kKV>;
+  using L = BwdLayout<D, kKV, kMask>;
   CUtensorMap map_q, map_k, map_v, map_do;
   if (int rc = make_tile_map(&map_q, p.q, kFp16, p.bh, p.t_q, D, kTile)) return rc;
   if (int rc = make_tile_map(&map_k, p.k, kFp16, p.bh, p.t_k, D, kTile)) return rc;
   if (int rc = make_tile_map(&map_v, p.v, kFp16, p.bh, p.t_k, D, kTile)) return rc;
   if (int rc = make_tile_map(&map_do, p.dout, kFp16, p.bh, p.t_q, D, kTile)) return rc;
   BwdParams prm;
+  prm.mask = static_cast<const unsigned short*>(p.mask);
   prm.lse = static_cast<const float*>(p.lse_in);
   prm.delta = static_cast<const float*>(p.delta);
   prm.out0 = kKV ? p.dk : p.dq;
@@ -646,7 +690,7 @@ int launch_bwd(const Problem& p) {
   prm.scale = static_cast<float>(p.scale);
   const long long ctas = p.bh * (kKV ? prm.kv_tiles : prm.q_tiles);
   if (ctas > 0x7fffffffLL) return fail(LIMN_B200_UNSUPPORTED, "sdpa backward: %lld CTAs exceed one grid", ctas);
-  auto kernel = sdpa_bwd_kernel<D, kCausal, kFp16, kKV, kEarly>;
+  auto kernel = sdpa_bwd_kernel<D, kCausal, kFp16, kKV, kEarly, kMask>;
   // the attribute is per device and per kernel instantiation; set it on first use there
   static bool sized[64] = {};
   int device = 0;
@@ -662,11 +706,16 @@ int launch_bwd(const Problem& p) {
   return LIMN_B200_OK;
 }
 
+template <int D, bool kKV, bool kMask>
+int launch_bwd_m(const Problem& p) {
+  const bool fp16 = p.dtype == LIMN_B200_F16;
+  if (p.causal) return fp16 ? launch_bwd<D, true, true, kKV, kMask>(p) : launch_bwd<D, true, false, kKV, kMask>(p);
+  return fp16 ? launch_bwd<D, false, true, kKV, kMask>(p) : launch_bwd<D, false, false, kKV, kMask>(p);
+}
+
 template <int D, bool kKV>
 int launch_bwd_d(const Problem& p) {
-  const bool fp16 = p.dtype == LIMN_B200_F16;
-  if (p.causal) return fp16 ? launch_bwd<D, true, true, kKV>(p) : launch_bwd<D, true, false, kKV>(p);
-  return fp16 ? launch_bwd<D, false, true, kKV>(p) : launch_bwd<D, false, false, kKV>(p);
+  return p.mask ? launch_bwd_m<D, kKV, true>(p) : launch_bwd_m<D, kKV, false>(p);
 }
 
 }  // namespace

@@ -1,4 +1,4 @@
-// "sdpa" forward for f16/bf16 with hd == hd_v in {64, 128}: TMA-staged tiles, tcgen05 MMAs
+// "sdpa" forward for f16/bf16 with hd == hd_v in {64, 128}, with or without a key mask: TMA-staged tiles, tcgen05 MMAs
 // accumulating in tensor memory, online softmax with one thread per query row.
 //
 // One CTA owns two consecutive tiles of 128 query rows of one (batch, head) problem and
@@ -51,7 +51,8 @@ struct FwdLayout {
   static constexpr int kKOff = kQOff + kQTiles * kTileBytes;
   static constexpr int kVOff = kKOff + kStages * kTileBytes;
   static constexpr int kBarOff = kVOff + kStages * kTileBytes;
-  static constexpr int kBytes = kBarOff + 256 + 1024;       // barriers + slack to align the base to 1024
+  static constexpr int kBiasOff = kBarOff + 256;            // key-mask kernels: [8 warps][2 buffers][128] floats, 0 or -inf per key
+  static constexpr int kBytes = kBiasOff + 8 * 1024 + 1024;  // + slack to align the base to 1024
   // tensor-memory columns
   static constexpr int kSCol = 0;                           // S_t at kSCol + 128 t (P_t overlays its first 64)
   static constexpr int kOCol = 256;                         // O_t at kOCol + D t
@@ -85,6 +86,7 @@ struct FwdParams {
 #ifdef LIMN_TRACE
   long long* trace;
 #endif
+  const unsigned short* mask;  // (bh, t_k) key flags in the storage dtype, 0 hides a key; null without a mask
   void* out;
   float* lse;
   unsigned* status;
@@ -94,7 +96,7 @@ struct FwdParams {
   float scale;
 };
 
-template <int D, bool kCausal, bool kFp16>
+template <int D, bool kCausal, bool kFp16, bool kMask>
 __global__ void __launch_bounds__(kThreads, 1)
 sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const FwdParams prm) {
@@ -284,7 +286,27 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     float m = -INFINITY, l = 0.f;
     const int n = n_kv[t];
     const uint64_t sl2_2 = f2_pack(sl2, sl2);
+    // Key mask: a hidden key is a score of -inf for every row. Each warp keeps its own copy of the tile's 128
+    // flags in shared memory as an additive 0 / -inf, each lane fetching four of them one tile ahead of use.
+    float* bias = reinterpret_cast<float*>(smem_unaligned + (base - raw) + L::kBiasOff) + warp * 256;
+    auto fetch_flags = [&](int kv0, float (&out4)[4]) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int key = kv0 + 32 * c + lane;
+        const bool live = key < prm.t_k && (prm.mask[static_cast<long long>(problem) * prm.t_k + key] & 0x7fffu) != 0;
+        out4[c] = live ? 0.f : -INFINITY;
+      }
+    };
+    float flags[4] = {0.f, 0.f, 0.f, 0.f};
+    if (kMask && n > 0) fetch_flags(0, flags);
     for (int j = 0; j < n; ++j) {
+      if (kMask) {
+        float* mine = bias + (j & 1) * 128;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) mine[32 * c + lane] = flags[c];
+        __syncwarp();
+        if (j + 1 < n) fetch_flags((j + 1) * kTileRows, flags);
+      }
       ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full + t), j & 1, prm.status, 0x0300u | t));  // warp-uniform: the tensor-memory ops below are warp-wide
       if (!ok) break;
       TRACE_EVENT(2);
@@ -306,40 +328,54 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           for (int i = 0; i < 32; ++i)
             if (c * 32 + i >= limit) s[c][i] = 0xff800000u;  // -inf
       }
+      if (kMask) {
+        const float2* mine = reinterpret_cast<const float2*>(bias + (j & 1) * 128);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float2 b = mine[(c * 32 + i) >> 1];
+            float lo, hi;
+            f2_unpack(f2_add(f2_pack_bits(s[c][i], s[c][i + 1]), f2_pack(b.x, b.y)), lo, hi);
+            s[c][i] = __float_as_uint(lo), s[c][i + 1] = __float_as_uint(hi);
+          }
+      }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int c = 0; c < 4; ++c)
 #pragma unroll
         for (int i = 0; i < 32; i += 2) mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      // the first tile always has a visible key (key 0), so mx is finite from the start
-      const bool moves = (mx - m) * sl2 > kRescaleSlack;  // true on the first tile, where m is -inf
+      // Without a key mask the first tile always has a visible key (key 0), so mx is finite from the start.
+      // With one, a row may have met no visible key yet: then mx and m are both -inf, nothing moves, and the
+      // exponentials are measured against 0 so that they come out exp2(-inf) = 0 instead of NaN.
+      const bool moves = (mx - m) * sl2 > kRescaleSlack;  // true at the first visible key, where m is -inf
       float alpha = 1.f;
       if (moves) {
         alpha = exp2_approx((m - mx) * sl2);
         m = mx;
       }
       TRACE_EVENT(4);
-      const float shift = -m * sl2;
+      const float shift = (kMask && m == -INFINITY) ? 0.f : -m * sl2;
       const uint64_t shift2 = f2_pack(shift, shift);
       uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         if (h == 1) {
-        // O_t was last written by the PV of tile j-1, which s_full also covers. It is rescaled before any of
-        // this tile's P_t is handed over (the product on the first half starts early), at the point where
-        // the first half's scores are no longer held in registers.
-        if (j > 0 && __any_sync(0xffffffffu, moves)) {
-  #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t o[32];
-            tmem_ld32(t_o + 32 * c, o);
-            tmem_ld_wait();
-  #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st32(t_o + 32 * c, o);
+          // O_t was last written by the PV of tile j-1, which s_full also covers. It is rescaled before any of
+          // this tile's P_t is handed over (the product on the first half starts early), at the point where
+          // the first half's scores are no longer held in registers.
+          if (j > 0 && __any_sync(0xffffffffu, moves)) {
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t o[32];
+              tmem_ld32(t_o + 32 * c, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st32(t_o + 32 * c, o);
+            }
           }
-        }
         }
         uint32_t packed[32];
 #pragma unroll
@@ -421,7 +457,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   }
 }
 
-template <int D, bool kCausal, bool kFp16>
+template <int D, bool kCausal, bool kFp16, bool kMask>
 int launch_fwd(const Problem& p) {
   using L = FwdLayout<D>;
   CUtensorMap map_q, map_k, map_v;
@@ -430,6 +466,7 @@ int launch_fwd(const Problem& p) {
   if (int rc = make_tile_map(&map_v, p.v, kFp16, p.bh, p.t_k, D, kTileRows)) return rc;
   FwdParams prm;
   prm.out = p.out;
+  prm.mask = static_cast<const unsigned short*>(p.mask);
   prm.lse = static_cast<float*>(p.lse_out);
   prm.status = p.status;
   if (prm.status == nullptr)
@@ -443,7 +480,7 @@ int launch_fwd(const Problem& p) {
   prm.scale = static_cast<float>(p.scale);
   const long long ctas = p.bh * prm.q_pairs;
   if (ctas > 0x7fffffffLL) return fail(LIMN_B200_UNSUPPORTED, "sdpa: %lld CTAs exceed one grid", ctas);
-  auto kernel = sdpa_fwd_kernel<D, kCausal, kFp16>;
+  auto kernel = sdpa_fwd_kernel<D, kCausal, kFp16, kMask>;
   // the attribute is per device and per kernel instantiation; set it on first use there
   static bool sized[64] = {};
   int device = 0;
@@ -459,11 +496,16 @@ int launch_fwd(const Problem& p) {
   return LIMN_B200_OK;
 }
 
+template <int D, bool kMask>
+int launch_fwd_m(const Problem& p) {
+  const bool fp16 = p.dtype == LIMN_B200_F16;
+  if (p.causal) return fp16 ? launch_fwd<D, true, true, kMask>(p) : launch_fwd<D, true, false, kMask>(p);
+  return fp16 ? launch_fwd<D, false, true, kMask>(p) : launch_fwd<D, false, false, kMask>(p);
+}
+
 template <int D>
 int launch_fwd_d(const Problem& p) {
-  const bool fp16 = p.dtype == LIMN_B200_F16;
-  if (p.causal) return fp16 ? launch_fwd<D, true, true>(p) : launch_fwd<D, true, false>(p);
-  return fp16 ? launch_fwd<D, false, true>(p) : launch_fwd<D, false, false>(p);
+  return p.mask ? launch_fwd_m<D, true>(p) : launch_fwd_m<D, false>(p);
 }
 
 }  // namespace

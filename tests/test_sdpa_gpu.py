@@ -124,6 +124,65 @@ def test_every_tail_length_d64_bf16(t, dev):
         close(dv, want_dv, 2e-2, f"t={t} dV")
 
 
+MASK_CASES = [
+    # id, shape (q = k = v), causal, mask kind
+    ("d64 full, keys hidden at random", (2, 3, 300, 64), False, "holes"),
+    ("d128 causal, padded batch", (3, 384, 128), True, "pad"),
+    ("d128 full, padded batch, ragged", (2, 200, 128), False, "pad"),
+    ("d64 causal, keys hidden at random", (2, 2, 257, 64), True, "holes"),
+]
+
+
+@pytest.mark.parametrize("case", MASK_CASES, ids=[c[0] for c in MASK_CASES])
+@pytest.mark.parametrize("dtype", [BF16, np.float16], ids=["bf16", "f16"])
+def test_key_mask_on_the_tensor_core_path(case, dtype, dev):
+    """A key mask with 16-bit storage: same kernels, hidden keys as -inf scores; dK and dV of a hidden key
+    are exact zeros (the reference's own test of that: tests/test_attention.py:112-119 there)."""
+    from limn_b200 import host
+
+    _, shape, causal, kind = case
+    rng = np.random.default_rng(len(shape) * 1000 + shape[-2])
+    q, k, v, do = (rng.standard_normal(shape).astype(np.float32).astype(dtype) for _ in range(4))
+    t_k = shape[-2]
+    if kind == "holes":
+        mask = (rng.random(shape[:-1]) > 0.3).astype(np.float32)
+        mask[..., 0] = 1  # under causal, row 0 sees key 0 only
+    else:
+        mask = np.broadcast_to((np.arange(t_k) < t_k * 2 // 3).astype(np.float32), shape[:-1]).copy()
+    mask = mask.astype(dtype)
+    scale = shape[-1] ** -0.5
+    name = "bfloat16" if dtype == BF16 else "float16"
+    att = host.Attention(dev, q, k, v, causal=causal, key_mask=mask)
+    out, lse = att.forward()
+    want_out, want_lse = oracle.sdpa_forward(q, k, v, mask, causal=causal, scale=scale)
+    close(out, want_out, FWD_TOL[name], "O")
+    close(lse, want_lse, LSE_TOL, "L")
+    dq, dk, dv = att.backward(do)
+    delta = oracle.row_delta(do, want_out)
+    want_dq = oracle.sdpa_backward_q(q, k, v, do, want_lse, delta, mask, causal=causal, scale=scale)
+    want_dk, want_dv = oracle.sdpa_backward_kv(q, k, v, do, want_lse, delta, mask, causal=causal, scale=scale)
+    for got, want, what in ((dq, want_dq, "dQ"), (dk, want_dk, "dK"), (dv, want_dv, "dV")):
+        close(got, want, BWD_TOL[name], what)
+    hidden = mask.astype(np.float32) == 0
+    assert (dk.astype(np.float32)[hidden] == 0).all() and (dv.astype(np.float32)[hidden] == 0).all()
+
+
+def test_masked_row_without_a_visible_key_on_the_tensor_core_path(dev):
+    """Causal with the first 5 keys hidden: rows 0-4 see nothing and come back NaN with L = -inf, the rest
+    are ordinary (limn/sdpa.py:111-112)."""
+    from limn_b200 import host
+
+    rng = np.random.default_rng(77)
+    q, k, v = (rng.standard_normal((2, 200, 64)).astype(np.float32).astype(BF16) for _ in range(3))
+    mask = np.ones((2, 200), np.float32)
+    mask[:, :5] = 0
+    out, lse = host.Attention(dev, q, k, v, causal=True, key_mask=mask.astype(BF16)).forward()
+    want_out, want_lse = oracle.sdpa_forward(q, k, v, mask.astype(BF16), causal=True, scale=0.125)
+    assert np.isnan(out.astype(np.float32)[:, :5]).all() and np.isneginf(lse[:, :5]).all()
+    assert oracle.worst(out.astype(np.float32)[:, 5:], want_out.astype(np.float32)[:, 5:]) <= 2e-2
+    assert float(np.abs(lse[:, 5:] - want_lse[:, 5:]).max()) <= 1e-3
+
+
 def test_two_runs_give_the_same_bits(dev):
     from limn_b200 import host
 
@@ -169,7 +228,8 @@ def test_tensor_core_path_is_the_one_that_serves_the_tuned_shapes():
     assert path(2, 256, 256, 256, 64, 64, 1, 0, 0.125) == PATH_TCGEN05
     assert path(1, 4, 100, 300, 64, 64, 0, 0, 0.125) == PATH_TCGEN05
     assert path(0, 2, 128, 128, 32, 32, 1, 0, 32**-0.5) == PATH_GENERAL
-    assert path(2, 2, 128, 128, 64, 64, 0, 1, 0.125) == PATH_GENERAL
+    assert path(2, 2, 128, 128, 64, 64, 0, 1, 0.125) == PATH_TCGEN05  # a key mask stays on the tensor-core path
+    assert path(0, 2, 128, 128, 64, 64, 0, 1, 0.125) == PATH_GENERAL
 
 
 def test_launch_errors_surface_as_runtime_errors(dev):
