@@ -95,6 +95,7 @@ struct BwdBars {
 #endif
 
 struct BwdParams {
+  long long bh;
 #ifdef LIMN_TRACE
   long long* trace;
 #endif
@@ -157,8 +158,8 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
   // ---- the tile this CTA owns and the range of tiles it streams ----
   const int own_tiles = kKV ? prm.kv_tiles : prm.q_tiles;
-  const int problem = blockIdx.x / own_tiles;
-  const int slot = blockIdx.x - problem * own_tiles;
+  int problem, slot;
+  cta_work(blockIdx.x, own_tiles, prm.bh, problem, slot);
   // longest streams first: under causal the last query tile sees every key tile, the first key tile every query tile
   const int own = (kCausal && !kKV) ? own_tiles - 1 - slot : slot;
   const int own0 = own * kTile;
@@ -681,6 +682,7 @@ int launch_bwd(const Problem& p) {
   prm.status = p.status;
   if (prm.status == nullptr)
     if (int rc = status_word(&prm.status)) return rc;
+  prm.bh = p.bh;
   prm.t_q = p.t_q, prm.t_k = p.t_k;
   prm.q_tiles = (p.t_q + kTile - 1) / kTile;
   prm.kv_tiles = (p.t_k + kTile - 1) / kTile;

@@ -83,6 +83,7 @@ struct FwdBars {
 #endif
 
 struct FwdParams {
+  long long bh;
 #ifdef LIMN_TRACE
   long long* trace;
 #endif
@@ -115,8 +116,9 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const int lane = threadIdx.x & 31;
 
   // ---- which rows this CTA owns ----
-  const int problem = blockIdx.x / prm.q_pairs;
-  const int pair = prm.q_pairs - 1 - (blockIdx.x - problem * prm.q_pairs);  // longest causal rows first
+  int problem, slot;
+  cta_work(blockIdx.x, prm.q_pairs, prm.bh, problem, slot);
+  const int pair = prm.q_pairs - 1 - slot;  // longest causal rows first
   int n_kv[kQTiles];  // key tiles each Q tile consumes
   int q0[kQTiles];
 #pragma unroll
@@ -471,6 +473,7 @@ int launch_fwd(const Problem& p) {
   prm.status = p.status;
   if (prm.status == nullptr)
     if (int rc = status_word(&prm.status)) return rc;
+  prm.bh = p.bh;
   prm.t_q = p.t_q, prm.t_k = p.t_k;
   prm.q_pairs = (p.t_q + kQTiles * kTileRows - 1) / (kQTiles * kTileRows);
   prm.kv_tiles = (p.t_k + kTileRows - 1) / kTileRows;
