@@ -252,6 +252,7 @@ class Shard:
             self.dq, self.dk, self.dv = (torch.empty(shape, dtype=torch.int16, device=device) for _ in range(3))
             self.grad_host = [torch.empty(shape, dtype=torch.int16).pin_memory() for _ in range(3)]
         self.launches = 0
+        self.pipeline = None
 
     def _check(self, code: int, doing: str) -> None:
         if code != 0:
@@ -277,20 +278,20 @@ class Shard:
             self.backward_pass()
 
     def step_from_host(self) -> tuple[int, int]:
-        """One step with host buffers: inputs come up from pinned memory, results go back down."""
-        up = down = 0
-        for pinned, dev in zip(self.pinned, self.dev):
-            nbytes = pinned.numel() * 2
-            self._check(self.lib.limn_b200_copy_h2d(dev.data_ptr(), pinned.data_ptr(), nbytes, None), "uploading inputs")
-            up += nbytes
-        self.step()
-        results = [(self.out_host, self.out), (self.lse_host, self.lse)]
-        if self.backward:
-            results += list(zip(self.grad_host, (self.dq, self.dk, self.dv)))
-        for host, dev in results:
-            nbytes = host.numel() * host.element_size()
-            self._check(self.lib.limn_b200_copy_d2h(host.data_ptr(), dev.data_ptr(), nbytes, None), "downloading results")
-            down += nbytes
+        """One step with host buffers, through limn_b200.hostio.HostPipeline: inputs come up from pinned
+        memory and results go back down to pinned memory, chunk by chunk, the copies overlapped with the
+        kernels on three streams. Returns (bytes uploaded, bytes downloaded)."""
+        if self.pipeline is None:
+            from limn_b200.hostio import HostPipeline
+
+            self.pipeline = HostPipeline(self.count, self.s, self.d, causal=self.causal, backward=self.backward, chunk=16)
+            self.host_in = [t.numpy() for t in self.pinned]
+            self.host_out = [self.out_host.numpy()] + ([t.numpy() for t in self.grad_host] if self.backward else [])
+            self.host_lse = self.lse_host.numpy()
+        q, k, v = self.host_in[:3]
+        extra = dict(do=self.host_in[3], dq=self.host_out[1], dk=self.host_out[2], dv=self.host_out[3]) if self.backward else {}
+        up, down = self.pipeline(q, k, v, self.host_out[0], self.host_lse, **extra)
+        self.launches += self.pipeline.launches
         return up, down
 
     def flops_per_step(self) -> float:

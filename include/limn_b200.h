@@ -125,6 +125,9 @@ int limn_b200_host_free(void* pinned_ptr);
 int limn_b200_copy_h2d(void* device_dst, const void* host_src, unsigned long long nbytes, void* stream);
 int limn_b200_copy_d2h(void* host_dst, const void* device_src, unsigned long long nbytes, void* stream);
 int limn_b200_copy_d2d(void* device_dst, const void* device_src, unsigned long long nbytes, void* stream);
+int limn_b200_stream_create(void** stream);
+int limn_b200_stream_destroy(void* stream);
+int limn_b200_stream_wait_event(void* stream, void* event);
 int limn_b200_stream_sync(void* stream);
 int limn_b200_device_sync(void);
 int limn_b200_event_create(void** event);

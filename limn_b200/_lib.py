@@ -42,6 +42,9 @@ SIGNATURES = {
     "limn_b200_copy_h2d": (c_int, (_P, _P, c_ulonglong, _P)),
     "limn_b200_copy_d2h": (c_int, (_P, _P, c_ulonglong, _P)),
     "limn_b200_copy_d2d": (c_int, (_P, _P, c_ulonglong, _P)),
+    "limn_b200_stream_create": (c_int, (POINTER(c_void_p),)),
+    "limn_b200_stream_destroy": (c_int, (_P,)),
+    "limn_b200_stream_wait_event": (c_int, (_P, _P)),
     "limn_b200_stream_sync": (c_int, (_P,)),
     "limn_b200_device_sync": (c_int, ()),
     "limn_b200_event_create": (c_int, (POINTER(c_void_p),)),

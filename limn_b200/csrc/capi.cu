@@ -266,6 +266,24 @@ int limn_b200_copy_d2d(void* device_dst, const void* device_src, unsigned long l
             "copying bytes on the device");
   return LIMN_B200_OK;
 }
+int limn_b200_stream_create(void** stream) {
+  clear_error();
+  cudaStream_t s;
+  LIMN_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking), "creating a stream");
+  *stream = s;
+  return LIMN_B200_OK;
+}
+int limn_b200_stream_destroy(void* stream) {
+  clear_error();
+  LIMN_CUDA(cudaStreamDestroy(static_cast<cudaStream_t>(stream)), "destroying a stream");
+  return LIMN_B200_OK;
+}
+int limn_b200_stream_wait_event(void* stream, void* event) {
+  clear_error();
+  LIMN_CUDA(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), static_cast<cudaEvent_t>(event), 0),
+            "making a stream wait for an event");
+  return LIMN_B200_OK;
+}
 int limn_b200_stream_sync(void* stream) {
   clear_error();
   LIMN_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)), "waiting for a stream");

@@ -88,7 +88,8 @@ class Event:
         self.handle = handle.value
 
     def record(self, stream=None) -> None:
-        check(lib().limn_b200_event_record(self.handle, stream), "recording an event")
+        handle = stream.handle if isinstance(stream, Stream) else stream
+        check(lib().limn_b200_event_record(self.handle, handle), "recording an event")
 
     def ms_since(self, start: "Event") -> float:
         ms = ctypes.c_float()
@@ -98,5 +99,48 @@ class Event:
     def __del__(self) -> None:
         try:
             lib().limn_b200_event_destroy(self.handle)
+        except Exception:
+            pass
+
+
+class Stream:
+    """A non-blocking CUDA stream (it does not synchronise with the legacy default stream)."""
+
+    def __init__(self) -> None:
+        handle = ctypes.c_void_p()
+        check(lib().limn_b200_stream_create(ctypes.byref(handle)), "creating a stream")
+        self.handle = handle.value
+
+    def wait(self, event: Event) -> None:
+        check(lib().limn_b200_stream_wait_event(self.handle, event.handle), "making a stream wait for an event")
+
+    def synchronize(self) -> None:
+        check(lib().limn_b200_stream_sync(self.handle), "waiting for a stream")
+
+    def __del__(self) -> None:
+        try:
+            lib().limn_b200_stream_destroy(self.handle)
+        except Exception:
+            pass
+
+
+class PinnedArray:
+    """Page-locked host memory viewed as a numpy array: what asynchronous copies need at the host end."""
+
+    def __init__(self, shape, dtype) -> None:
+        self.dtype = np.dtype(dtype)
+        self.nbytes = int(np.prod(shape)) * self.dtype.itemsize
+        ptr = ctypes.c_void_p()
+        check(lib().limn_b200_host_alloc(ctypes.byref(ptr), self.nbytes), f"allocating {self.nbytes} pinned bytes")
+        self.ptr = ptr.value
+        raw = (ctypes.c_ubyte * self.nbytes).from_address(self.ptr)
+        self.array = np.frombuffer(raw, dtype=np.uint8).view(self.dtype).reshape(shape)
+
+    def __del__(self) -> None:
+        try:
+            if self.ptr:
+                self.array = None
+                lib().limn_b200_host_free(self.ptr)
+                self.ptr = 0
         except Exception:
             pass
