@@ -8,12 +8,16 @@
 // key tiles j of 128 keys:
 //     S  = Q K_j^T            (both K-major)            -> tensor memory, fp32
 //     dP = dO V_j^T           (both K-major)            -> tensor memory, fp32
-//     dS = exp2(S*c - L) * (dP - delta)  by 256 threads -> tensor memory, 16-bit, over dP
+//     dS = exp2(S*c - L) * (dP - delta)  by 256 threads -> tensor memory, 16-bit, in columns of its own
 //     dQ += dS K_j            (A from tensor memory, B = the same K_j tile read MN-major)
 // sdpa_bwd_kv: a CTA owns 128 keys (K and V tiles stay) and streams query tiles i:
 //     S^T  = K Q_i^T, dP^T = V dO_i^T                   -> tensor memory (keys on the lanes)
 //     P^T, dS^T as above, per-query L and delta read from shared memory
 //     dV += P^T dO_i, dK += dS^T Q_i   (A from tensor memory, B = the streamed tiles MN-major)
+// Two schedules (template kEarly, see the kernel): where tensor memory has room for the 16-bit operands
+// beside the scores (the dQ pass, and the dK/dV pass at head dim 64) the next tile's full-width scores are
+// issued as soon as this tile's are in registers; otherwise the operands overlay the scores and the tile
+// is pipelined as two 64-column halves. A key mask (hidden key = -inf score) is served by both.
 // The scale is applied once to dQ and dK when they are written (oracle: limn/sdpa.py:157-170,
 // :190-203, where ds carries the scale per element; the products are the same up to rounding).
 //
