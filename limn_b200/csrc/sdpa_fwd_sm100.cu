@@ -38,7 +38,7 @@ constexpr uint32_t kTmemCols = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleSlack = 8.f;   // log2 units a row maximum may outgrow its reference before O is rescaled
 #ifndef LIMN_POLY_PAIRS
-#define LIMN_POLY_PAIRS 0
+#define LIMN_POLY_PAIRS 2
 #endif
 constexpr int kPolyPairsOf8 = LIMN_POLY_PAIRS;       // of every 8 pairs of scores, how many take exp2 on the FMA pipe instead of the SFU
 
@@ -387,7 +387,9 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           for (int i = 0; i < 32; i += 2) {
             const uint64_t x2 = f2_fma(f2_pack_bits(s[c][i], s[c][i + 1]), sl2_2, shift2);
             float p0, p1;
-            if (((i >> 1) & 7) < kPolyPairsOf8) {
+            // (not under a key mask: the cubic turns a hidden key's -inf into 2^-125 rather than 0, which a row
+            // with no visible key at all would then mistake for a denominator)
+            if (!kMask && ((i >> 1) & 7) < kPolyPairsOf8) {
               exp2_poly2(x2, p0, p1);
             } else {
               f2_unpack(x2, p0, p1);
