@@ -14,10 +14,10 @@
 //     S^T  = K Q_i^T, dP^T = V dO_i^T                   -> tensor memory (keys on the lanes)
 //     P^T, dS^T as above, per-query L and delta read from shared memory
 //     dV += P^T dO_i, dK += dS^T Q_i   (A from tensor memory, B = the streamed tiles MN-major)
-// Two schedules (template kEarly, see the kernel): where tensor memory has room for the 16-bit operands
-// beside the scores (the dQ pass, and the dK/dV pass at head dim 64) the next tile's full-width scores are
-// issued as soon as this tile's are in registers; otherwise the operands overlay the scores and the tile
-// is pipelined as two 64-column halves. A key mask (hidden key = -inf score) is served by both.
+// Two schedules (templates kEarly / kSeq, see the kernel): where tensor memory has room for S, dP and the
+// 16-bit operands side by side (the dQ pass, and the dK/dV pass at head dim 64) the next tile's scores are
+// issued as soon as this tile's are in registers; in the dK/dV pass at head dim 128 S^T and dP^T take turns in
+// one region instead. Every MMA is full width (N = 128 or D). A key mask (hidden key = -inf score) is served by both.
 // The scale is applied once to dQ and dK when they are written (oracle: limn/sdpa.py:157-170,
 // :190-203, where ds carries the scale per element; the products are the same up to rounding).
 //
@@ -74,6 +74,8 @@ struct BwdLayout {
   static constexpr int kAcc1 = 256 + D;  // dK
   static constexpr int kDsCol = 448;     // early schedule: dS (or dS^T) as 16-bit, 64 columns
   static constexpr int kPtCol = 384;     // early schedule, dK/dV pass at head dim 64: P^T as 16-bit, 64 columns
+  static constexpr int kSeqPtCol = 128;  // sequential schedule: P^T, 64 columns (S^T and dP^T share columns 0-127)
+  static constexpr int kSeqDsCol = 192;  // sequential schedule: dS^T, 64 columns
 };
 
 template <int D, bool kKV, bool kMask>
@@ -86,7 +88,8 @@ struct BwdBars {
   static constexpr int b_empty = b_full + kSB;
   static constexpr int s_full = b_empty + kSB;    // + half: that half's columns of S and dP are ready
   static constexpr int ds_full = s_full + 2;      // + half: its 16-bit operands are written (128 arrivals)
-  static constexpr int acc_full = ds_full + 2;
+  static constexpr int extra = ds_full + 2;       // + 0/1, sequential schedule: S^T / dP^T are in registers (256 arrivals)
+  static constexpr int acc_full = extra + 2;
   static constexpr int count = acc_full + 1;
 };
 
@@ -135,12 +138,13 @@ __device__ __forceinline__ void store_row32(void* base, long long elem_offset, c
 }
 
 // kKV = false: sdpa_bwd_q (CTA owns query rows, streams K/V). kKV = true: sdpa_bwd_kv.
-// kEarly picks the schedule. true: the 16-bit operands get tensor-memory columns of their own, so the next
-// tile's full-width (N = 128) scores are issued as soon as this tile's have been read into registers and
-// run beside the elementwise stage; it needs 64 (dQ pass) or 128 (dK/dV pass) spare columns, which the
-// dK/dV pass has only at head dim 64. false: the operands overlay the scores and the tile is pipelined in
-// two 64-column halves instead.
-template <int D, bool kCausal, bool kFp16, bool kKV, bool kEarly, bool kMask>
+// Exactly one of kEarly and kSeq is set; they pick the schedule. kEarly: S and dP have their own 128 columns
+// each and the 16-bit operands columns of their own too, so the next tile's scores are issued as soon as this
+// tile's have been read into registers and run beside the elementwise stage; it needs 64 (dQ pass) or 128
+// (dK/dV pass) columns beyond scores and accumulators, which the dK/dV pass has only at head dim 64. kSeq (the dK/dV pass at head dim 128, where all 512 columns are spoken for):
+// S^T and dP^T take turns in one 128-column region, S^T first, dP^T as soon as S^T is in registers, so that
+// 128 columns are left for the operands and every MMA is full width.
+template <int D, bool kCausal, bool kFp16, bool kKV, bool kEarly, bool kSeq, bool kMask>
 __global__ void __launch_bounds__(kThreads, 1)
 sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
@@ -180,11 +184,13 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     abort_flag = *reinterpret_cast<volatile unsigned*>(prm.status) != kStatusOk;
     for (int i = 0; i < B::count; ++i) {
       uint32_t arrivals = 1u;
-      if (kEarly) {
+      if (kSeq) {
+        // s_full + 0/1: S^T / dP^T ready; extra + 0/1: read into registers; ds_full: operands stored;
+        // ds_full + 1: products done (one commit)
+        if (i == B::extra || i == B::extra + 1 || i == B::ds_full) arrivals = 256u;
+      } else if (kEarly) {
         // s_full + 1 doubles as "scores read into registers", ds_full + 1 as "products done" (one commit)
         if (i == B::s_full + 1 || i == B::ds_full) arrivals = 256u;
-      } else if (i == B::ds_full || i == B::ds_full + 1) {
-        arrivals = 128u;
       }
       mbar_init(bar(i), arrivals);
     }
@@ -255,49 +261,63 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   } else if (warp == kMmaWarp) {
     // ================= MMA issuer =================
     if (lane == 0) {
-      constexpr uint32_t idesc_s = mma_idesc(kTile, kTile / 2, kFp16, false, false);
       constexpr uint32_t idesc_acc = mma_idesc(kTile, D, kFp16, false, true);
-      // One half (64 columns) of S and of dP for the streamed tile in `stage`: C[128 x 64] = A B^T over the
-      // head dim, A a resident tile, B rows [64 half, 64 half + 64) of a streamed tile, both K-major.
-      auto issue_scores = [&](int half, int stage) {
-        const uint32_t b_row = half * 64 * 128;
+      if constexpr (kSeq) {
+        constexpr uint32_t idesc_full = mma_idesc(kTile, kTile, kFp16, false, false);
         constexpr uint32_t kAtom16 = L::kAtomBytes >> 4;
-        const uint32_t a0 = desc_lo(held_a_smem, 0), b0 = desc_lo(stream_a_smem(stage) + b_row, 0);
-        const uint32_t a1 = desc_lo(held_b_smem, 0), b1 = desc_lo(stream_b_smem(stage) + b_row, 0);
-        const uint32_t c0 = tmem + L::kSCol + half * 64, c1 = tmem + L::kPCol + half * 64;
-        mma_ss_lo<false>(c0, a0, b0, idesc_s);
+        // C[128 x 128] = A B^T over the head dim into the shared score columns
+        auto issue_score = [&](uint32_t a_tile, uint32_t b_tile, int which) {
+          const uint32_t a0 = desc_lo(a_tile, 0), b0 = desc_lo(b_tile, 0);
+          mma_ss_lo<false>(tmem + L::kSCol, a0, b0, idesc_full);
 #pragma unroll
-        for (int kk = 1; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * kAtom16 + (kk % 4) * 2;  // in 16-byte units
-          mma_ss_lo<true>(c0, a0 + off, b0 + off, idesc_s);
-        }
-        mma_ss_lo<false>(c1, a1, b1, idesc_s);
+          for (int kk = 1; kk < D / 16; ++kk) {
+            const uint32_t off = (kk / 4) * kAtom16 + (kk % 4) * 2;
+            mma_ss_lo<true>(tmem + L::kSCol, a0 + off, b0 + off, idesc_full);
+          }
+          mma_commit(bar(B::s_full + which));
+        };
+        auto issue_acc_full = [&](uint32_t c_col, uint32_t a_col, uint32_t b_tile, bool fresh) {
+          const uint32_t b_lo = desc_lo(b_tile, L::kAtomBytes);
 #pragma unroll
-        for (int kk = 1; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * kAtom16 + (kk % 4) * 2;
-          mma_ss_lo<true>(c1, a1 + off, b1 + off, idesc_s);
+          for (int kk = 0; kk < kTile / 16; ++kk)
+            mma_ts_lo(tmem + c_col, tmem + a_col + kk * 8, b_lo + kk * (16 * 128 / 16), idesc_acc, (kk > 0 || !fresh) ? 1u : 0u);
+        };
+        auto wait_tile = [&](int it) {
+          bool got = mbar_wait(a_full(it), a_wrap(it), prm.status, 0x1210u);
+          if (got) got = mbar_wait(b_full(it), b_wrap(it), prm.status, 0x1211u);
+          return got;
+        };
+        ok = mbar_wait(bar(B::held_full), 0, prm.status, 0x1200u);
+        if (ok) ok = wait_tile(0);
+        if (ok) {
+          tc_fence_after_sync();
+          issue_score(held_a_smem, stream_a_smem(0), 0);  // S^T = K Q_0^T
         }
-        mma_commit(bar(B::s_full + half));
-      };
-      // C[128 x D] += A B over 64 rows of a streamed tile: A 16-bit in tensor memory at a_col + 64 half
-      // (32 columns), B rows [64 half, +64) of the tile read MN-major, 16 rows per instruction.
-      auto issue_acc = [&](uint32_t c_col, uint32_t a_col, uint32_t b_tile, int half, bool fresh) {
-        const uint32_t b_lo = desc_lo(b_tile + half * 64 * 128, L::kAtomBytes);
-        const uint32_t a = tmem + a_col + half * 64;
-        const uint32_t c = tmem + c_col;
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          mma_ts_lo(c, a + kk * 8, b_lo + kk * (16 * 128 / 16), idesc_acc, (kk > 0 || !fresh) ? 1u : 0u);
-      };
-      auto issue_products = [&](int half, int stage, bool fresh) {
-        if (kKV) {
-          issue_acc(L::kAcc0, L::kSCol, stream_b_smem(stage), half, fresh);  // dV += P^T dO_i
-          issue_acc(L::kAcc1, L::kPCol, stream_a_smem(stage), half, fresh);  // dK += dS^T Q_i
-        } else {
-          issue_acc(L::kAcc0, L::kPCol, stream_a_smem(stage), half, fresh);  // dQ += dS K_j
+        for (int it = 0; it < count && ok; ++it) {
+          // dP^T takes the score columns as soon as S^T has been read out of them
+          ok = mbar_wait(bar(B::extra + 0), it & 1, prm.status, 0x1260u);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_score(held_b_smem, stream_b_smem(it), 1);  // dP^T = V dO_i^T
+          // and the next tile's S^T as soon as dP^T has been read
+          ok = mbar_wait(bar(B::extra + 1), it & 1, prm.status, 0x1261u);
+          if (!ok) break;
+          if (it + 1 < count) {
+            ok = wait_tile(it + 1);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_score(held_a_smem, stream_a_smem(it + 1), 0);
+          }
+          ok = mbar_wait(bar(B::ds_full), it & 1, prm.status, 0x1220u);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_acc_full(L::kAcc0, L::kSeqPtCol, stream_b_smem(it), it == 0);  // dV += P^T dO_i
+          issue_acc_full(L::kAcc1, L::kSeqDsCol, stream_a_smem(it), it == 0);  // dK += dS^T Q_i
+          mma_commit(bar(B::ds_full + 1));  // products done: the operand columns may be rewritten
+          mma_commit(a_empty(it));
+          mma_commit(b_empty(it));
         }
-      };
-      if constexpr (kEarly) {
+      } else if constexpr (kEarly) {
         constexpr uint32_t idesc_full = mma_idesc(kTile, kTile, kFp16, false, false);
         constexpr uint32_t kAtom16 = L::kAtomBytes >> 4;
         // S and dP of the whole streamed tile: C[128 x 128] = A B^T over the head dim
@@ -360,48 +380,6 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           mma_commit(a_empty(it));
           if (kKV) mma_commit(b_empty(it));
         }
-      } else {
-        auto wait_tile = [&](int it) {
-          bool got = mbar_wait(a_full(it), a_wrap(it), prm.status, 0x1210u);
-          if (got) got = mbar_wait(b_full(it), b_wrap(it), prm.status, 0x1211u);
-          return got;
-        };
-        ok = mbar_wait(bar(B::held_full), 0, prm.status, 0x1200u);
-        if (ok) ok = wait_tile(0);
-        if (ok) {
-          tc_fence_after_sync();
-          issue_scores(0, 0);
-          issue_scores(1, 0);
-        }
-        // Steady state, per streamed tile: as soon as a half's 16-bit operands are back, its products are
-        // issued and then the same half of the next tile's scores, so the other half's elementwise work
-        // always has MMAs running beside it.
-        for (int it = 0; it < count && ok; ++it) {
-          const bool more = it + 1 < count;
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            TRACE_EVENT(100 + half);
-            ok = mbar_wait(bar(B::ds_full + half), it & 1, prm.status, 0x1220u | half);
-            if (!ok) break;
-            TRACE_EVENT(110 + half);
-            tc_fence_after_sync();
-            issue_products(half, it, it == 0 && half == 0);
-            TRACE_EVENT(120 + half);
-            if (half == 1) {
-              mma_commit(a_empty(it));
-              mma_commit(b_empty(it));
-            }
-            if (more) {
-              if (half == 0) {
-                ok = wait_tile(it + 1);
-                if (!ok) break;
-                tc_fence_after_sync();
-              }
-              issue_scores(half, it + 1);
-              TRACE_EVENT(130 + half);
-            }
-          }
-        }
       }
       if (ok) mma_commit(bar(B::acc_full));
     }
@@ -428,14 +406,14 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     // dK/dV pass: the statistics of the streamed tile's queries. Every warp keeps its own copy of its group's
     // 64 columns in shared memory (-L log2e then -delta), each lane fetching two columns of each from global
     // memory one tile ahead of their use, so no warp ever waits for another here.
+    // A warp issues in order, so nothing may depend on these loads until the next tile: the raw values are
+    // parked in registers and negated, scaled and range-checked only when they are staged.
     struct Fetched { float l0, l1, d0, d1; };
     auto fetch_stat = [&](int tile0) {
       Fetched f;
-      const int q0 = tile0 + group * 64 + lane, q1 = q0 + 32;
-      f.l0 = q0 < prm.t_q ? -prm.lse[stat_base + q0] * kLog2e : -INFINITY;
-      f.l1 = q1 < prm.t_q ? -prm.lse[stat_base + q1] * kLog2e : -INFINITY;
-      f.d0 = q0 < prm.t_q ? -prm.delta[stat_base + q0] : 0.f;
-      f.d1 = q1 < prm.t_q ? -prm.delta[stat_base + q1] : 0.f;
+      const int q0 = min(tile0 + group * 64 + lane, prm.t_q - 1), q1 = min(tile0 + group * 64 + lane + 32, prm.t_q - 1);
+      f.l0 = prm.lse[stat_base + q0], f.l1 = prm.lse[stat_base + q1];
+      f.d0 = prm.delta[stat_base + q0], f.d1 = prm.delta[stat_base + q1];
       return f;
     };
     Fetched fetched = {0.f, 0.f, 0.f, 0.f};
@@ -471,12 +449,83 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
       }
       if (kKV) {
-        st[lane] = fetched.l0, st[lane + 32] = fetched.l1;
-        st[64 + lane] = fetched.d0, st[96 + lane] = fetched.d1;
+        const bool in0 = other0 + group * 64 + lane < prm.t_q, in1 = other0 + group * 64 + lane + 32 < prm.t_q;
+        st[lane] = in0 ? -fetched.l0 * kLog2e : -INFINITY, st[lane + 32] = in1 ? -fetched.l1 * kLog2e : -INFINITY;
+        TRACE_EVENT(8);
+        st[64 + lane] = in0 ? -fetched.d0 : 0.f, st[96 + lane] = in1 ? -fetched.d1 : 0.f;
         __syncwarp();
+        TRACE_EVENT(9);
         if (it + 1 < count) fetched = fetch_stat(other0 + kTile);
       }
-      if constexpr (kEarly) {
+      if constexpr (kSeq) {
+        // S^T and dP^T arrive one after the other in the same columns; the probabilities wait in registers
+        TRACE_EVENT(1);
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full + 0), it & 1, prm.status, 0x1300u | group));
+        if (!ok) continue;
+        TRACE_EVENT(2);
+        tc_fence_after_sync();
+        uint32_t s[2][32];
+        tmem_ld32(t_s + group * 64, s[0]);
+        tmem_ld32(t_s + group * 64 + 32, s[1]);
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        mbar_arrive(bar(B::extra + 0));  // dP^T may overwrite S^T
+        TRACE_EVENT(3);
+        if (kCausal && other0 == own0) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (group * 64 + c * 32 + e < r) s[c][e] = 0xff800000u;  // query before key: probability exactly 0
+        }
+        uint32_t p_packed[32];
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const float2 a = *reinterpret_cast<const float2*>(st + c * 32 + e);
+            uint64_t neg_l2 = f2_pack(a.x, a.y);
+            if (kMask) neg_l2 = f2_add(neg_l2, row_bias2);
+            float p0, p1;
+            f2_unpack(f2_fma(f2_pack_bits(s[c][e], s[c][e + 1]), sl2_2, neg_l2), p0, p1);
+            p0 = exp2_approx(p0), p1 = exp2_approx(p1);
+            s[c][e] = __float_as_uint(p0), s[c][e + 1] = __float_as_uint(p1);  // kept for dS
+            p_packed[c * 16 + (e >> 1)] = kFp16 ? pack_f16(p0, p1) : pack_bf16(p0, p1);
+          }
+        TRACE_EVENT(4);
+        // the previous tile's products must have consumed the operand columns before they are rewritten
+        if (it > 0) {
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(B::ds_full + 1), (it - 1) & 1, prm.status, 0x1320u | group));
+          if (!ok) continue;
+          tc_fence_after_sync();
+        }
+        tmem_st32(tmem + lane_base + L::kSeqPtCol + group * 32, p_packed);
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full + 1), it & 1, prm.status, 0x1330u | group));
+        if (!ok) continue;
+        tc_fence_after_sync();
+        uint32_t dp[2][32];
+        tmem_ld32(t_s + group * 64, dp[0]);
+        tmem_ld32(t_s + group * 64 + 32, dp[1]);
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        mbar_arrive(bar(B::extra + 1));  // the next tile's S^T may overwrite dP^T
+        uint32_t ds_packed[32];
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const float2 b = *reinterpret_cast<const float2*>(st + 64 + c * 32 + e);
+            float d0, d1;
+            f2_unpack(f2_mul(f2_pack_bits(s[c][e], s[c][e + 1]), f2_add(f2_pack_bits(dp[c][e], dp[c][e + 1]), f2_pack(b.x, b.y))), d0, d1);
+            ds_packed[c * 16 + (e >> 1)] = kFp16 ? pack_f16(d0, d1) : pack_bf16(d0, d1);
+          }
+        tmem_st32(tmem + lane_base + L::kSeqDsCol + group * 32, ds_packed);
+        tmem_st_wait();
+        TRACE_EVENT(5);
+        tc_fence_before_sync();
+        mbar_arrive(bar(B::ds_full));
+        TRACE_EVENT(7);
+      } else if constexpr (kEarly) {
         TRACE_EVENT(1);
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full), it & 1, prm.status, 0x1300u | group));
         if (!ok) continue;
@@ -556,70 +605,6 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         TRACE_EVENT(5);
         tc_fence_before_sync();
         mbar_arrive(bar(B::ds_full));
-      } else {
-        TRACE_EVENT(1);
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full + group), it & 1, prm.status, 0x1300u | group));
-        if (!ok) continue;
-        TRACE_EVENT(2);
-        tc_fence_after_sync();
-        // which (lane, column) pairs take part: causal diagonal tile, and keys past t_k in the dQ pass
-        const bool diagonal = kCausal && other0 == own0;
-        const bool ragged = !kKV && other0 + kTile > prm.t_k;
-  #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const int col0 = group * 64 + c * 32;
-          uint32_t s[32], dp[32];
-          tmem_ld32(t_s + col0, s);
-          tmem_ld32(t_p + col0, dp);
-          tmem_ld_wait();
-          TRACE_EVENT(3 + c * 10);
-          if (diagonal || ragged) {
-  #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              const int col = col0 + e;
-              bool hidden = false;
-              if (diagonal) hidden = kKV ? (col < r) : (col > r);   // a key index must not exceed the query index
-              if (ragged) hidden = hidden || (other0 + col >= prm.t_k);
-              if (hidden) s[e] = 0xff800000u;  // -inf: the probability becomes exactly 0
-            }
-          }
-          uint32_t p_packed[16], ds_packed[16];
-  #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            uint64_t neg_l2, neg_delta;
-            if (kKV) {
-              const float2 a = *reinterpret_cast<const float2*>(st + c * 32 + e);
-              const float2 b = *reinterpret_cast<const float2*>(st + 64 + c * 32 + e);
-              neg_l2 = f2_pack(a.x, a.y);
-              neg_delta = f2_pack(b.x, b.y);
-            } else {
-              neg_l2 = row_neg_l2;
-              neg_delta = row_neg_delta;
-            }
-            float x0, x1;
-            if (kMask) {
-              if (kKV) {
-                neg_l2 = f2_add(neg_l2, row_bias2);
-              } else {
-                const float2 b = *reinterpret_cast<const float2*>(st + c * 32 + e);
-                neg_l2 = f2_add(neg_l2, f2_pack(b.x, b.y));
-              }
-            }
-            f2_unpack(f2_fma(f2_pack_bits(s[e], s[e + 1]), sl2_2, neg_l2), x0, x1);
-            const float p0 = exp2_approx(x0), p1 = exp2_approx(x1);
-            float d0, d1;
-            f2_unpack(f2_mul(f2_pack(p0, p1), f2_add(f2_pack_bits(dp[e], dp[e + 1]), neg_delta)), d0, d1);
-            if (kKV) p_packed[e >> 1] = kFp16 ? pack_f16(p0, p1) : pack_bf16(p0, p1);
-            ds_packed[e >> 1] = kFp16 ? pack_f16(d0, d1) : pack_bf16(d0, d1);
-          }
-          if (kKV) tmem_st16(t_s + group * 64 + c * 16, p_packed);
-          tmem_st16(t_p + group * 64 + c * 16, ds_packed);
-          TRACE_EVENT(4 + c * 10);
-        }
-        tmem_st_wait();
-        TRACE_EVENT(5);
-        tc_fence_before_sync();
-        mbar_arrive(bar(B::ds_full + group));
       }
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::acc_full), 0, prm.status, 0x1310u));
@@ -670,7 +655,8 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
 template <int D, bool kCausal, bool kFp16, bool kKV, bool kMask>
 int launch_bwd(const Problem& p) {
-  constexpr bool kEarly = !kKV || D == 64;  // the dK/dV pass at head dim 128 has no spare tensor-memory columns
+  constexpr bool kEarly = !kKV || D == 64;  // the dK/dV pass at head dim 128 has no spare tensor-memory columns ...
+  constexpr bool kSeq = !kEarly;            // ... so there S^T and dP^T share one region, one after the other
   using L = BwdLayout<D, kKV, kMask>;
   CUtensorMap map_q, map_k, map_v, map_do;
   if (int rc = make_tile_map(&map_q, p.q, kFp16, p.bh, p.t_q, D, kTile)) return rc;
@@ -696,7 +682,7 @@ int launch_bwd(const Problem& p) {
   prm.scale = static_cast<float>(p.scale);
   const long long ctas = p.bh * (kKV ? prm.kv_tiles : prm.q_tiles);
   if (ctas > 0x7fffffffLL) return fail(LIMN_B200_UNSUPPORTED, "sdpa backward: %lld CTAs exceed one grid", ctas);
-  auto kernel = sdpa_bwd_kernel<D, kCausal, kFp16, kKV, kEarly, kMask>;
+  auto kernel = sdpa_bwd_kernel<D, kCausal, kFp16, kKV, kEarly, kSeq, kMask>;
   // the attribute is per device and per kernel instantiation; set it on first use there
   static bool sized[64] = {};
   int device = 0;
