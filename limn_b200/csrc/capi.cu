@@ -58,6 +58,37 @@ int status_word(unsigned int** word) {
   return LIMN_B200_OK;
 }
 
+int schedule_words(unsigned int** pair) {
+  static unsigned int* rings[kMaxDevices] = {};
+  static unsigned next[kMaxDevices] = {};
+  int device = 0;
+  LIMN_CUDA(cudaGetDevice(&device), "asking for the current device");
+  if (device < 0 || device >= kMaxDevices) return fail(LIMN_B200_UNSUPPORTED, "device ordinal %d out of range", device);
+  std::lock_guard<std::mutex> lock(g_status_mutex);
+  if (rings[device] == nullptr) {
+    unsigned int* fresh = nullptr;
+    LIMN_CUDA(cudaMalloc(&fresh, kScheduleRing * 2 * sizeof(unsigned)), "allocating the work counters");
+    LIMN_CUDA(cudaMemset(fresh, 0, kScheduleRing * 2 * sizeof(unsigned)), "clearing the work counters");
+    rings[device] = fresh;
+  }
+  *pair = rings[device] + 2 * (next[device]++ % kScheduleRing);
+  return LIMN_B200_OK;
+}
+
+int sm_count(int* count) {
+  static int cached[kMaxDevices] = {};
+  int device = 0;
+  LIMN_CUDA(cudaGetDevice(&device), "asking for the current device");
+  if (device < 0 || device >= kMaxDevices) return fail(LIMN_B200_UNSUPPORTED, "device ordinal %d out of range", device);
+  if (cached[device] == 0) {
+    int n = 0;
+    LIMN_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device), "asking for the SM count");
+    cached[device] = n;
+  }
+  *count = cached[device];
+  return LIMN_B200_OK;
+}
+
 int make_tile_map(CUtensorMap* map, const void* base, bool fp16, long long bh, int rows, int width, int box_rows) {
   std::call_once(g_encode_once, [] {
     void* fn = nullptr;

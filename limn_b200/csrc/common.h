@@ -33,6 +33,8 @@ struct Problem {
   cudaStream_t stream = nullptr;
   // Where kernels that wait record giving up. Null means the per-device word status_word() allocates.
   unsigned int* status = nullptr;
+  // Two zeroed words for the kernels' work counters. Null means a pair from schedule_words().
+  unsigned int* schedule = nullptr;
 };
 
 enum class Op { Fwd, BwdQ, BwdKV };
@@ -53,6 +55,13 @@ int cuda_fail(cudaError_t err, const char* doing);
 // Device address of the current device's status word (allocated on first use, one per
 // device, zero-initialised). Kernels that wait write a non-zero code there when they give up.
 int status_word(unsigned int** word);
+// Two zeroed words (next work item, CTAs finished) for one launch of a kernel whose CTAs fetch their
+// work items themselves. A kernel leaves its pair zeroed again, so the pairs are handed out in turn from
+// a fixed per-device ring; a pair is only met twice by launches kScheduleRing apart.
+constexpr int kScheduleRing = 128;
+int schedule_words(unsigned int** pair);
+// Streaming multiprocessors of the current device.
+int sm_count(int* count);
 
 // Argument checks and dispatch shared by every entry point for the three ops.
 int dispatch_op(Op op, const char* name, const Problem& p);

@@ -90,7 +90,11 @@ struct BwdBars {
   static constexpr int ds_full = s_full + 2;      // + half: its 16-bit operands are written (128 arrivals)
   static constexpr int extra = ds_full + 2;       // + 0/1, sequential schedule: S^T / dP^T are in registers (256 arrivals)
   static constexpr int acc_full = extra + 2;
-  static constexpr int count = acc_full + 1;
+  static constexpr int acc_free = acc_full + 1;     // the epilogue has read the accumulators (256 arrivals)
+  static constexpr int held_empty = acc_free + 1;   // the item's last scores are computed: the resident tiles may be replaced
+  static constexpr int work_full = held_empty + 1;  // + slot: the producer has fetched a work item
+  static constexpr int work_empty = work_full + 2;  // + slot: every consumer has read it
+  static constexpr int count = work_empty + 2;
 };
 
 // Build-time diagnostic (-DLIMN_TRACE): one CTA records clock64() at each step of its pipeline into a
@@ -112,6 +116,8 @@ struct BwdParams {
   void* out0;   // dQ, or dK
   void* out1;   // dV
   unsigned* status;
+  unsigned* schedule;  // [0] next work item, [1] CTAs that have finished; both zero between launches
+  unsigned items;      // work items: bh * (tiles of 128 rows a problem's owner side has)
   int t_q, t_k;
   int q_tiles, kv_tiles;
   float scale;
@@ -154,6 +160,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   extern __shared__ unsigned char smem_unaligned[];
   __shared__ uint32_t tmem_slot;
   __shared__ uint32_t abort_flag;
+  __shared__ unsigned work_ring[2];
 
   const uint32_t base = (smem_addr(smem_unaligned) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_unaligned + (base - smem_addr(smem_unaligned));
@@ -164,21 +171,30 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  // ---- the tile this CTA owns and the range of tiles it streams ----
+  // ---- a work item: the tile of 128 rows it owns and the range of tiles streamed past it ----
   const int own_tiles = kKV ? prm.kv_tiles : prm.q_tiles;
-  int problem, slot;
-  cta_work(blockIdx.x, own_tiles, prm.bh, problem, slot);
-  // longest streams first: under causal the last query tile sees every key tile, the first key tile every query tile
-  const int own = (kCausal && !kKV) ? own_tiles - 1 - slot : slot;
-  const int own0 = own * kTile;
-  int first, count;
-  if (kKV) {
-    first = kCausal ? own : 0;
-    count = prm.q_tiles - first;
-  } else {
-    first = 0;
-    count = kCausal ? min(prm.kv_tiles, own + 1) : prm.kv_tiles;
-  }
+  struct Item {
+    int problem;
+    int own0;    // first owned row
+    int first;   // first streamed tile
+    int count;   // streamed tiles
+  };
+  auto decode = [&](unsigned index) {
+    Item item;
+    int slot;
+    cta_work(static_cast<int>(index), own_tiles, prm.bh, item.problem, slot);
+    // longest streams first: under causal the last query tile sees every key tile, the first key tile every query tile
+    const int own = (kCausal && !kKV) ? own_tiles - 1 - slot : slot;
+    item.own0 = own * kTile;
+    if (kKV) {
+      item.first = kCausal ? own : 0;
+      item.count = prm.q_tiles - item.first;
+    } else {
+      item.first = 0;
+      item.count = kCausal ? min(prm.kv_tiles, own + 1) : prm.kv_tiles;
+    }
+    return item;
+  };
 
   if (threadIdx.x == 0) {
     abort_flag = *reinterpret_cast<volatile unsigned*>(prm.status) != kStatusOk;
@@ -192,13 +208,14 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         // s_full + 1 doubles as "scores read into registers", ds_full + 1 as "products done" (one commit)
         if (i == B::s_full + 1 || i == B::ds_full) arrivals = 256u;
       }
+      if (i == B::acc_free) arrivals = 256u;
+      if (i == B::work_empty || i == B::work_empty + 1) arrivals = 9u;  // the MMA warp and the eight elementwise warps
       mbar_init(bar(i), arrivals);
     }
     mbar_init_fence();
   }
   __syncthreads();
-  if (abort_flag) return;
-  if (warp == kMmaWarp) {
+  if (warp == kMmaWarp && !abort_flag) {
     tmem_alloc(smem_addr(&tmem_slot), kTmemCols);
     tmem_relinquish();
   }
@@ -223,45 +240,72 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   auto a_wrap = [&](int it) { return static_cast<uint32_t>((it / L::kStagesA) & 1); };
   auto b_wrap = [&](int it) { return static_cast<uint32_t>((it / L::kStagesB) & 1); };
 
-  bool ok = true;
+  bool ok = !abort_flag;  // an earlier kernel on this device gave up: take no work, only leave the counters as found
 #ifdef LIMN_TRACE
   int trace_n = 0;
 #endif
   TRACE_EVENT(0);
 
+  // The grid is one CTA per SM. The producer fetches work items from a counter and passes them to the other
+  // warps through a two-entry ring, so the next item's tiles are on their way while the current item is still
+  // being computed. Every role walks the same items in the same order; `done` counts the streamed tiles of
+  // the items before the current one, and rings and per-tile barrier phases are keyed by done + it.
+  auto next_item = [&](unsigned n_item, unsigned& index) {
+    const unsigned ring = n_item & 1u;
+    if (!mbar_wait(bar(B::work_full + ring), (n_item >> 1) & 1u, prm.status, 0x1400u | ring)) return false;
+    index = *reinterpret_cast<volatile unsigned*>(&work_ring[ring]);
+    return true;
+  };
+
   if (warp == kProducerWarp) {
-    // ================= TMA producer =================
-    if (lane == 0) {
+    // ================= TMA producer, work fetcher =================
+    if (lane == 0 && ok) {
       tma_prefetch_descriptor(held_a);
       tma_prefetch_descriptor(held_b);
       tma_prefetch_descriptor(stream_a);
       tma_prefetch_descriptor(stream_b);
-      mbar_expect_tx(bar(B::held_full), 2 * L::kTileBytes);
-#pragma unroll
-      for (int a = 0; a < D / 64; ++a) {
-        tma_load_3d(held_a_smem + a * L::kAtomBytes, held_a, bar(B::held_full), a * 64, own0, problem);
-        tma_load_3d(held_b_smem + a * L::kAtomBytes, held_b, bar(B::held_full), a * 64, own0, problem);
-      }
-      for (int it = 0; it < count; ++it) {
-        const int row0 = (first + it) * kTile;
-        ok = mbar_wait(a_empty(it), a_wrap(it) ^ 1u, prm.status, 0x1100u);
+      int done = 0;
+      for (unsigned n_item = 0; ok; ++n_item) {
+        const unsigned ring = n_item & 1u;
+        ok = mbar_wait(bar(B::work_empty + ring), ((n_item >> 1) & 1u) ^ 1u, prm.status, 0x1120u | ring);
         if (!ok) break;
-        mbar_expect_tx(a_full(it), L::kTileBytes);
-#pragma unroll
-        for (int a = 0; a < D / 64; ++a)
-          tma_load_3d(stream_a_smem(it) + a * L::kAtomBytes, stream_a, a_full(it), a * 64, row0, problem);
-        ok = mbar_wait(b_empty(it), b_wrap(it) ^ 1u, prm.status, 0x1110u);
+        const unsigned index = atomicAdd(prm.schedule, 1u);
+        *reinterpret_cast<volatile unsigned*>(&work_ring[ring]) = index;
+        mbar_arrive(bar(B::work_full + ring));
+        if (index >= prm.items) break;
+        const Item item = decode(index);
+        ok = mbar_wait(bar(B::held_empty), (n_item & 1u) ^ 1u, prm.status, 0x1130u);
         if (!ok) break;
-        mbar_expect_tx(b_full(it), L::kTileBytes);
+        mbar_expect_tx(bar(B::held_full), 2 * L::kTileBytes);
 #pragma unroll
-        for (int a = 0; a < D / 64; ++a)
-          tma_load_3d(stream_b_smem(it) + a * L::kAtomBytes, stream_b, b_full(it), a * 64, row0, problem);
+        for (int a = 0; a < D / 64; ++a) {
+          tma_load_3d(held_a_smem + a * L::kAtomBytes, held_a, bar(B::held_full), a * 64, item.own0, item.problem);
+          tma_load_3d(held_b_smem + a * L::kAtomBytes, held_b, bar(B::held_full), a * 64, item.own0, item.problem);
+        }
+        for (int it = 0; it < item.count; ++it) {
+          const int g = done + it;
+          const int row0 = (item.first + it) * kTile;
+          ok = mbar_wait(a_empty(g), a_wrap(g) ^ 1u, prm.status, 0x1100u);
+          if (!ok) break;
+          mbar_expect_tx(a_full(g), L::kTileBytes);
+#pragma unroll
+          for (int a = 0; a < D / 64; ++a)
+            tma_load_3d(stream_a_smem(g) + a * L::kAtomBytes, stream_a, a_full(g), a * 64, row0, item.problem);
+          ok = mbar_wait(b_empty(g), b_wrap(g) ^ 1u, prm.status, 0x1110u);
+          if (!ok) break;
+          mbar_expect_tx(b_full(g), L::kTileBytes);
+#pragma unroll
+          for (int a = 0; a < D / 64; ++a)
+            tma_load_3d(stream_b_smem(g) + a * L::kAtomBytes, stream_b, b_full(g), a * 64, row0, item.problem);
+        }
+        done += item.count;
       }
     }
   } else if (warp == kMmaWarp) {
     // ================= MMA issuer =================
-    if (lane == 0) {
+    if (lane == 0 && ok) {
       constexpr uint32_t idesc_acc = mma_idesc(kTile, D, kFp16, false, true);
+      int done = 0;
       if constexpr (kSeq) {
         constexpr uint32_t idesc_full = mma_idesc(kTile, kTile, kFp16, false, false);
         constexpr uint32_t kAtom16 = L::kAtomBytes >> 4;
@@ -287,35 +331,49 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           if (got) got = mbar_wait(b_full(it), b_wrap(it), prm.status, 0x1211u);
           return got;
         };
-        ok = mbar_wait(bar(B::held_full), 0, prm.status, 0x1200u);
-        if (ok) ok = wait_tile(0);
-        if (ok) {
-          tc_fence_after_sync();
-          issue_score(held_a_smem, stream_a_smem(0), 0);  // S^T = K Q_0^T
-        }
-        for (int it = 0; it < count && ok; ++it) {
-          // dP^T takes the score columns as soon as S^T has been read out of them
-          ok = mbar_wait(bar(B::extra + 0), it & 1, prm.status, 0x1260u);
+        for (unsigned n_item = 0; ok; ++n_item) {
+          unsigned index;
+          ok = next_item(n_item, index);
+          if (!ok) break;
+          mbar_arrive(bar(B::work_empty + (n_item & 1u)));
+          if (index >= prm.items) break;
+          const int count = decode(index).count;
+          ok = mbar_wait(bar(B::held_full), n_item & 1u, prm.status, 0x1200u);
+          if (ok) ok = wait_tile(done);
           if (!ok) break;
           tc_fence_after_sync();
-          issue_score(held_b_smem, stream_b_smem(it), 1);  // dP^T = V dO_i^T
-          // and the next tile's S^T as soon as dP^T has been read
-          ok = mbar_wait(bar(B::extra + 1), it & 1, prm.status, 0x1261u);
-          if (!ok) break;
-          if (it + 1 < count) {
-            ok = wait_tile(it + 1);
+          issue_score(held_a_smem, stream_a_smem(done), 0);  // S^T = K Q_0^T (the previous item's last dP^T has been read)
+          for (int it = 0; it < count && ok; ++it) {
+            const int g = done + it;
+            // dP^T takes the score columns as soon as S^T has been read out of them
+            ok = mbar_wait(bar(B::extra + 0), g & 1, prm.status, 0x1260u);
             if (!ok) break;
             tc_fence_after_sync();
-            issue_score(held_a_smem, stream_a_smem(it + 1), 0);
+            issue_score(held_b_smem, stream_b_smem(g), 1);  // dP^T = V dO_i^T
+            if (it + 1 == count) mma_commit(bar(B::held_empty));  // K and V have been read for the last time
+            // and the next tile's S^T as soon as dP^T has been read
+            ok = mbar_wait(bar(B::extra + 1), g & 1, prm.status, 0x1261u);
+            if (!ok) break;
+            if (it + 1 < count) {
+              ok = wait_tile(g + 1);
+              if (!ok) break;
+              tc_fence_after_sync();
+              issue_score(held_a_smem, stream_a_smem(g + 1), 0);
+            }
+            ok = mbar_wait(bar(B::ds_full), g & 1, prm.status, 0x1220u);
+            // the item's first products overwrite the accumulators: the previous item's epilogue must have read them
+            if (ok && it == 0) ok = mbar_wait(bar(B::acc_free), (n_item & 1u) ^ 1u, prm.status, 0x1270u);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_acc_full(L::kAcc0, L::kSeqPtCol, stream_b_smem(g), it == 0);  // dV += P^T dO_i
+            issue_acc_full(L::kAcc1, L::kSeqDsCol, stream_a_smem(g), it == 0);  // dK += dS^T Q_i
+            mma_commit(bar(B::ds_full + 1));  // products done: the operand columns may be rewritten
+            mma_commit(a_empty(g));
+            mma_commit(b_empty(g));
           }
-          ok = mbar_wait(bar(B::ds_full), it & 1, prm.status, 0x1220u);
           if (!ok) break;
-          tc_fence_after_sync();
-          issue_acc_full(L::kAcc0, L::kSeqPtCol, stream_b_smem(it), it == 0);  // dV += P^T dO_i
-          issue_acc_full(L::kAcc1, L::kSeqDsCol, stream_a_smem(it), it == 0);  // dK += dS^T Q_i
-          mma_commit(bar(B::ds_full + 1));  // products done: the operand columns may be rewritten
-          mma_commit(a_empty(it));
-          mma_commit(b_empty(it));
+          mma_commit(bar(B::acc_full));
+          done += count;
         }
       } else if constexpr (kEarly) {
         constexpr uint32_t idesc_full = mma_idesc(kTile, kTile, kFp16, false, false);
@@ -350,38 +408,54 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           if (got) got = mbar_wait(b_full(it), b_wrap(it), prm.status, 0x1211u);
           return got;
         };
-        ok = mbar_wait(bar(B::held_full), 0, prm.status, 0x1200u);
-        if (ok) ok = wait_tile(0);
-        if (ok) {
-          tc_fence_after_sync();
-          issue_scores_full(0);
-          if (!kKV) mma_commit(b_empty(0));  // dQ pass: V is read by the scores only
-        }
-        for (int it = 0; it < count && ok; ++it) {
-          if (it + 1 < count) {
-            // the next tile's scores may overwrite this tile's once every thread holds them in registers
-            ok = mbar_wait(bar(B::s_full + 1), it & 1, prm.status, 0x1240u);
-            if (ok) ok = wait_tile(it + 1);
-            if (!ok) break;
-            tc_fence_after_sync();
-            issue_scores_full(it + 1);
-            if (!kKV) mma_commit(b_empty(it + 1));
-          }
-          ok = mbar_wait(bar(B::ds_full), it & 1, prm.status, 0x1220u);
+        for (unsigned n_item = 0; ok; ++n_item) {
+          unsigned index;
+          ok = next_item(n_item, index);
+          if (!ok) break;
+          mbar_arrive(bar(B::work_empty + (n_item & 1u)));
+          if (index >= prm.items) break;
+          const int count = decode(index).count;
+          ok = mbar_wait(bar(B::held_full), n_item & 1u, prm.status, 0x1200u);
+          // the previous item's last scores must be in registers before this item's first overwrite them
+          if (ok && done > 0) ok = mbar_wait(bar(B::s_full + 1), (done - 1) & 1, prm.status, 0x1241u);
+          if (ok) ok = wait_tile(done);
           if (!ok) break;
           tc_fence_after_sync();
-          if (kKV) {
-            issue_acc_full(L::kAcc0, L::kPtCol, stream_b_smem(it), it == 0);  // dV += P^T dO_i
-            issue_acc_full(L::kAcc1, L::kDsCol, stream_a_smem(it), it == 0);  // dK += dS^T Q_i
-          } else {
-            issue_acc_full(L::kAcc0, L::kDsCol, stream_a_smem(it), it == 0);  // dQ += dS K_j
+          issue_scores_full(done);
+          if (!kKV) mma_commit(b_empty(done));  // dQ pass: V is read by the scores only
+          if (count == 1) mma_commit(bar(B::held_empty));
+          for (int it = 0; it < count && ok; ++it) {
+            const int g = done + it;
+            if (it + 1 < count) {
+              // the next tile's scores may overwrite this tile's once every thread holds them in registers
+              ok = mbar_wait(bar(B::s_full + 1), g & 1, prm.status, 0x1240u);
+              if (ok) ok = wait_tile(g + 1);
+              if (!ok) break;
+              tc_fence_after_sync();
+              issue_scores_full(g + 1);
+              if (!kKV) mma_commit(b_empty(g + 1));
+              if (it + 2 == count) mma_commit(bar(B::held_empty));  // the resident tiles have been read for the last time
+            }
+            ok = mbar_wait(bar(B::ds_full), g & 1, prm.status, 0x1220u);
+            // the item's first products overwrite the accumulators: the previous item's epilogue must have read them
+            if (ok && it == 0) ok = mbar_wait(bar(B::acc_free), (n_item & 1u) ^ 1u, prm.status, 0x1270u);
+            if (!ok) break;
+            tc_fence_after_sync();
+            if (kKV) {
+              issue_acc_full(L::kAcc0, L::kPtCol, stream_b_smem(g), it == 0);  // dV += P^T dO_i
+              issue_acc_full(L::kAcc1, L::kDsCol, stream_a_smem(g), it == 0);  // dK += dS^T Q_i
+            } else {
+              issue_acc_full(L::kAcc0, L::kDsCol, stream_a_smem(g), it == 0);  // dQ += dS K_j
+            }
+            mma_commit(bar(B::ds_full + 1));            // products done: the operand columns may be rewritten
+            mma_commit(a_empty(g));
+            if (kKV) mma_commit(b_empty(g));
           }
-          mma_commit(bar(B::ds_full + 1));            // products done: the operand columns may be rewritten
-          mma_commit(a_empty(it));
-          if (kKV) mma_commit(b_empty(it));
+          if (!ok) break;
+          mma_commit(bar(B::acc_full));
+          done += count;
         }
       }
-      if (ok) mma_commit(bar(B::acc_full));
     }
   } else {
     // ================= elementwise stage + epilogue: 2 groups x 128 threads =================
@@ -392,6 +466,16 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const uint32_t t_p = tmem + lane_base + L::kPCol;
     const float sl2 = prm.scale * kLog2e;
     const uint64_t sl2_2 = f2_pack(sl2, sl2);
+    int done = 0;
+    for (unsigned n_item = 0; ok; ++n_item) {
+    unsigned index;
+    ok = __all_sync(0xffffffffu, next_item(n_item, index));
+    if (!ok) break;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar(B::work_empty + (n_item & 1u)));
+    if (index >= prm.items) break;
+    const Item item = decode(index);
+    const int problem = item.problem, own0 = item.own0, first = item.first, count = item.count;
     const long long stat_base = static_cast<long long>(problem) * prm.t_q;
     // statistics enter negated: x = s * c + (-L log2e), t = dP + (-delta). A row or column past t_q
     // gets -L = -inf, which makes its probability exactly 0.
@@ -437,9 +521,10 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
     }
     for (int it = 0; it < count; ++it) {
+      const int g = done + it;                  // the tile's ordinal over all items: rings and barrier phases go by it
       const int other0 = (first + it) * kTile;  // first key (dQ pass) or first query (dK/dV pass) of the streamed tile
       // per warp: [2 buffers][-L log2e, -delta][64 columns]
-      float* st = stat + (warp * 2 + (it & 1)) * (2 * 64);
+      float* st = stat + (warp * 2 + (g & 1)) * (2 * 64);
       if (kMask && !kKV) {
         st[lane] = col_bias0, st[lane + 32] = col_bias1;
         __syncwarp();
@@ -460,7 +545,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       if constexpr (kSeq) {
         // S^T and dP^T arrive one after the other in the same columns; the probabilities wait in registers
         TRACE_EVENT(1);
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full + 0), it & 1, prm.status, 0x1300u | group));
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full + 0), g & 1, prm.status, 0x1300u | group));
         if (!ok) continue;
         TRACE_EVENT(2);
         tc_fence_after_sync();
@@ -494,13 +579,13 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
         TRACE_EVENT(4);
         // the previous tile's products must have consumed the operand columns before they are rewritten
-        if (it > 0) {
-          ok = __all_sync(0xffffffffu, mbar_wait(bar(B::ds_full + 1), (it - 1) & 1, prm.status, 0x1320u | group));
+        if (g > 0) {
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(B::ds_full + 1), (g - 1) & 1, prm.status, 0x1320u | group));
           if (!ok) continue;
           tc_fence_after_sync();
         }
         tmem_st32(tmem + lane_base + L::kSeqPtCol + group * 32, p_packed);
-        ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full + 1), it & 1, prm.status, 0x1330u | group));
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full + 1), g & 1, prm.status, 0x1330u | group));
         if (!ok) continue;
         tc_fence_after_sync();
         uint32_t dp[2][32];
@@ -527,7 +612,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         TRACE_EVENT(7);
       } else if constexpr (kEarly) {
         TRACE_EVENT(1);
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full), it & 1, prm.status, 0x1300u | group));
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full), g & 1, prm.status, 0x1300u | group));
         if (!ok) continue;
         TRACE_EVENT(2);
         tc_fence_after_sync();
@@ -594,8 +679,8 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
         TRACE_EVENT(4);
         // the previous tile's products must have consumed the operand columns before they are rewritten
-        if (it > 0) {
-          ok = __all_sync(0xffffffffu, mbar_wait(bar(B::ds_full + 1), (it - 1) & 1, prm.status, 0x1320u | group));
+        if (g > 0) {
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(B::ds_full + 1), (g - 1) & 1, prm.status, 0x1320u | group));
           if (!ok) continue;
           tc_fence_after_sync();
         }
@@ -607,7 +692,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         mbar_arrive(bar(B::ds_full));
       }
     }
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::acc_full), 0, prm.status, 0x1310u));
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::acc_full), n_item & 1u, prm.status, 0x1310u));
     if (ok) {
       tc_fence_after_sync();
       const int row = own0 + r;
@@ -638,18 +723,29 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           if (in) store_row32<kFp16>(prm.out0, out_row * D + col, acc, prm.scale);
         }
       }
+      // the accumulators are in registers or stored: the next item's first products may overwrite them
+      tc_fence_before_sync();
+      mbar_arrive(bar(B::acc_free));
     }
+    done += count;
+    }  // items
   }
 
   // ---- teardown ----
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == kMmaWarp) {
+  if (warp == kMmaWarp && !abort_flag) {
     if (*reinterpret_cast<volatile unsigned*>(prm.status) != kStatusOk) {
       for (int i = 0; i < 2000; ++i) __nanosleep(1000);  // let copies and MMAs still in flight land
     }
     tc_fence_after_sync();
     tmem_free(tmem, kTmemCols);
+  }
+  // the last CTA to leave puts the work counters back to zero for the next launch that is handed this pair
+  if (threadIdx.x == 0 && atomicAdd(prm.schedule + 1, 1u) == gridDim.x - 1) {
+    prm.schedule[0] = 0u;
+    prm.schedule[1] = 0u;
+    __threadfence();
   }
 }
 
@@ -680,8 +776,15 @@ int launch_bwd(const Problem& p) {
   prm.trace = reinterpret_cast<long long*>(strtoull(getenv("LIMN_TRACE_PTR"), nullptr, 16));
 #endif
   prm.scale = static_cast<float>(p.scale);
-  const long long ctas = p.bh * (kKV ? prm.kv_tiles : prm.q_tiles);
-  if (ctas > 0x7fffffffLL) return fail(LIMN_B200_UNSUPPORTED, "sdpa backward: %lld CTAs exceed one grid", ctas);
+  const long long items = p.bh * (kKV ? prm.kv_tiles : prm.q_tiles);
+  if (items > 0x7fffffffLL) return fail(LIMN_B200_UNSUPPORTED, "sdpa backward: %lld work items exceed the counter", items);
+  prm.items = static_cast<unsigned>(items);
+  prm.schedule = p.schedule;
+  if (prm.schedule == nullptr)
+    if (int rc = schedule_words(&prm.schedule)) return rc;
+  int sms = 0;
+  if (int rc = sm_count(&sms)) return rc;
+  const long long ctas = items < sms ? items : sms;  // one CTA per SM, each fetching items until none is left
   auto kernel = sdpa_bwd_kernel<D, kCausal, kFp16, kKV, kEarly, kSeq, kMask>;
   // the attribute is per device and per kernel instantiation; set it on first use there
   static bool sized[64] = {};

@@ -1,17 +1,21 @@
 // "sdpa" forward for f16/bf16 with hd == hd_v in {64, 128}, with or without a key mask: TMA-staged tiles, tcgen05 MMAs
 // accumulating in tensor memory, online softmax with one thread per query row.
 //
-// One CTA owns two consecutive tiles of 128 query rows of one (batch, head) problem and
-// streams that problem's keys and values past them in tiles of 128 keys:
+// A work item is two consecutive tiles of 128 query rows of one (batch, head) problem; the problem's keys
+// and values stream past them in tiles of 128 keys:
 //   S_t = Q_t K_j^T          tcgen05.mma, both operands K-major in shared memory, S_t in tensor memory
 //   P_t = exp2(S_t - m_t)    128 softmax threads per Q tile, one row each; P_t overwrites S_t as 16-bit
 //   O_t += P_t V_j           tcgen05.mma, A = P_t from tensor memory, B = V_j (MN-major) from shared memory
-// Two Q tiles per CTA keep the tensor pipe busy on one while the other is in its softmax.
+// Two Q tiles per item keep the tensor pipe busy on one while the other is in its softmax.
 // Each output row has exactly one owner and is accumulated in a fixed key order, so two
 // runs give the same bits, as the kernel this replaces promises (limn/cuda_emit.py:748-752).
 //
-// Warp roles (10 warps): 0-3 softmax/epilogue of Q tile 0, 4-7 of Q tile 1, 8 TMA producer,
-// 9 MMA issuer and tensor-memory owner.
+// The grid is one CTA per SM. A CTA fetches items from a counter (longest first) until none is left, so
+// barriers, tensor memory and descriptors are set up once, and the next item's Q, K and V are on their way
+// (and its first scores computed) while the current item's last tile and epilogue are still running.
+//
+// Warp roles (10 warps): 0-3 softmax/epilogue of Q tile 0, 4-7 of Q tile 1, 8 TMA producer and work
+// fetcher, 9 MMA issuer and tensor-memory owner.
 //
 // Semantics follow the oracle (limn/sdpa.py:91-137): causal keeps key j for row i when
 // j <= i; O is rounded once from the fp32 accumulator; L = m + log(l) in natural log.
@@ -31,7 +35,10 @@ using namespace ptx;
 
 constexpr int kTileRows = 128;   // query rows per Q tile, keys per K/V tile
 constexpr int kQTiles = 2;       // Q tiles per CTA
-constexpr int kThreads = 320;
+#ifndef LIMN_FWD_THREADS
+#define LIMN_FWD_THREADS 320
+#endif
+constexpr int kThreads = LIMN_FWD_THREADS;
 constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;
 constexpr uint32_t kTmemCols = 512;
@@ -71,7 +78,11 @@ struct FwdBars {
   static constexpr int p_full = s_full + 2;      // + t
   static constexpr int o_full = p_full + 2;      // + t
   static constexpr int p_half = o_full + 2;      // + t: the first 64 keys' worth of P_t is in place (and O_t rescaled)
-  static constexpr int count = p_half + 2;
+  static constexpr int q_empty = p_half + 2;     // + t: the item's last S_t has been computed, Q_t may be replaced
+  static constexpr int o_free = q_empty + 2;     // + t: the epilogue has read O_t, the next item may overwrite it
+  static constexpr int work_full = o_free + 2;   // + slot: the producer has fetched a work item
+  static constexpr int work_empty = work_full + 2;  // + slot: every consumer has read it
+  static constexpr int count = work_empty + 2;
 };
 
 // Build-time diagnostic (-DLIMN_TRACE): one CTA records clock64() at each step of its pipeline into a
@@ -91,8 +102,10 @@ struct FwdParams {
   void* out;
   float* lse;
   unsigned* status;
+  unsigned* schedule;  // [0] next work item, [1] CTAs that have finished; both zero between launches
+  unsigned items;      // work items: bh * q_pairs
   int t_q, t_k;
-  int q_pairs;      // CTAs per problem
+  int q_pairs;      // work items per problem
   int kv_tiles;     // ceil(t_k / 128)
   float scale;
 };
@@ -106,6 +119,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   extern __shared__ unsigned char smem_unaligned[];
   __shared__ uint32_t tmem_slot;
   __shared__ uint32_t abort_flag;
+  __shared__ unsigned work_ring[2];
 
   const uint32_t raw = smem_addr(smem_unaligned);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -115,33 +129,43 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  // ---- which rows this CTA owns ----
-  int problem, slot;
-  cta_work(blockIdx.x, prm.q_pairs, prm.bh, problem, slot);
-  const int pair = prm.q_pairs - 1 - slot;  // longest causal rows first
-  int n_kv[kQTiles];  // key tiles each Q tile consumes
-  int q0[kQTiles];
+  // ---- which rows a work item covers ----
+  struct Item {
+    int problem;
+    int q0[kQTiles];    // first query row of each Q tile
+    int n_kv[kQTiles];  // key tiles each Q tile consumes
+    int n_max;
+  };
+  auto decode = [&](unsigned index) {
+    Item it;
+    int slot;
+    cta_work(static_cast<int>(index), prm.q_pairs, prm.bh, it.problem, slot);
+    const int pair = prm.q_pairs - 1 - slot;  // longest causal rows first
 #pragma unroll
-  for (int t = 0; t < kQTiles; ++t) {
-    q0[t] = (pair * kQTiles + t) * kTileRows;
-    int n = prm.kv_tiles;
-    if (kCausal) n = min(n, pair * kQTiles + t + 1);
-    n_kv[t] = q0[t] < prm.t_q ? n : 0;
-  }
-  const int n_max = max(n_kv[0], n_kv[1]);
+    for (int t = 0; t < kQTiles; ++t) {
+      it.q0[t] = (pair * kQTiles + t) * kTileRows;
+      int n = prm.kv_tiles;
+      if (kCausal) n = min(n, pair * kQTiles + t + 1);
+      it.n_kv[t] = it.q0[t] < prm.t_q ? n : 0;
+    }
+    it.n_max = max(it.n_kv[0], it.n_kv[1]);
+    return it;
+  };
 
   // ---- set-up: barriers, tensor memory ----
   if (threadIdx.x == 0) {
     abort_flag = *reinterpret_cast<volatile unsigned*>(prm.status) != kStatusOk;
     for (int i = 0; i < B::count; ++i) {
-      const bool softmax_arrives = (i >= B::p_full && i < B::p_full + 2) || (i >= B::p_half && i < B::p_half + 2);
-      mbar_init(bar(i), softmax_arrives ? 128u : 1u);
+      unsigned arrivals = 1u;
+      if ((i >= B::p_full && i < B::p_full + 2) || (i >= B::p_half && i < B::p_half + 2) || (i >= B::o_free && i < B::o_free + 2))
+        arrivals = 128u;                                           // every thread of a softmax group
+      if (i >= B::work_empty && i < B::work_empty + 2) arrivals = 9u;  // the MMA warp and the eight softmax warps
+      mbar_init(bar(i), arrivals);
     }
     mbar_init_fence();
   }
   __syncthreads();
-  if (abort_flag) return;  // an earlier kernel on this device gave up; do not pile on
-  if (warp == kMmaWarp) {
+  if (warp == kMmaWarp && !abort_flag) {
     tmem_alloc(smem_addr(&tmem_slot), kTmemCols);
     tmem_relinquish();
   }
@@ -150,49 +174,74 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   tc_fence_after_sync();
   const uint32_t tmem = tmem_slot;
 
-  bool ok = true;
+  bool ok = !abort_flag;  // an earlier kernel on this device gave up: take no work, only leave the counters as found
 #ifdef LIMN_TRACE
   int trace_n = 0;
 #endif
   TRACE_EVENT(0);
 
+  // Work items are fetched by the producer and passed to the other warps through a two-entry ring, so
+  // the producer can load the next item's Q, K and V while the current item is still being computed.
+  // Every role walks the same items in the same order and counts its own barrier phases as it goes.
+  auto next_item = [&](unsigned n_item, unsigned& index) {
+    const unsigned slot = n_item & 1u;
+    if (!mbar_wait(bar(B::work_full + slot), (n_item >> 1) & 1u, prm.status, 0x0400u | slot)) return false;
+    index = *reinterpret_cast<volatile unsigned*>(&work_ring[slot]);
+    return true;
+  };
+
   if (warp == kProducerWarp) {
-    // ================= TMA producer =================
-    if (lane == 0) {
+    // ================= TMA producer, work fetcher =================
+    if (lane == 0 && ok) {
       tma_prefetch_descriptor(&map_q);
       tma_prefetch_descriptor(&map_k);
       tma_prefetch_descriptor(&map_v);
-#pragma unroll
-      for (int t = 0; t < kQTiles; ++t) {
-        if (n_kv[t] == 0) continue;
-        mbar_expect_tx(bar(B::q_full + t), L::kTileBytes);
-#pragma unroll
-        for (int a = 0; a < D / 64; ++a)
-          tma_load_3d(base + L::kQOff + t * L::kTileBytes + a * L::kAtomBytes, &map_q, bar(B::q_full + t), a * 64, q0[t],
-                      problem);
-      }
-      for (int j = 0; j < n_max && ok; ++j) {
-        const int stage = j % L::kStages;
-        const uint32_t wrap = (j / L::kStages) & 1;
-        ok = mbar_wait(bar(B::k_empty + stage), wrap ^ 1u, prm.status, 0x0100u | stage);
+      unsigned q_uses[kQTiles] = {0u, 0u};  // items so far in which Q tile t had rows
+      unsigned step = 0;                    // key tiles loaded so far, over all items
+      for (unsigned n_item = 0; ok; ++n_item) {
+        const unsigned slot = n_item & 1u;
+        ok = mbar_wait(bar(B::work_empty + slot), ((n_item >> 1) & 1u) ^ 1u, prm.status, 0x0120u | slot);
         if (!ok) break;
-        mbar_expect_tx(bar(B::k_full + stage), L::kTileBytes);
+        const unsigned index = atomicAdd(prm.schedule, 1u);
+        *reinterpret_cast<volatile unsigned*>(&work_ring[slot]) = index;
+        mbar_arrive(bar(B::work_full + slot));
+        if (index >= prm.items) break;
+        const Item item = decode(index);
 #pragma unroll
-        for (int a = 0; a < D / 64; ++a)
-          tma_load_3d(base + L::kKOff + stage * L::kTileBytes + a * L::kAtomBytes, &map_k, bar(B::k_full + stage), a * 64,
-                      j * kTileRows, problem);
-        ok = mbar_wait(bar(B::v_empty + stage), wrap ^ 1u, prm.status, 0x0110u | stage);
-        if (!ok) break;
-        mbar_expect_tx(bar(B::v_full + stage), L::kTileBytes);
+        for (int t = 0; t < kQTiles; ++t) {
+          if (item.n_kv[t] == 0 || !ok) continue;
+          ok = mbar_wait(bar(B::q_empty + t), (q_uses[t] & 1u) ^ 1u, prm.status, 0x0130u | t);
+          if (!ok) break;
+          ++q_uses[t];
+          mbar_expect_tx(bar(B::q_full + t), L::kTileBytes);
 #pragma unroll
-        for (int a = 0; a < D / 64; ++a)
-          tma_load_3d(base + L::kVOff + stage * L::kTileBytes + a * L::kAtomBytes, &map_v, bar(B::v_full + stage), a * 64,
-                      j * kTileRows, problem);
+          for (int a = 0; a < D / 64; ++a)
+            tma_load_3d(base + L::kQOff + t * L::kTileBytes + a * L::kAtomBytes, &map_q, bar(B::q_full + t), a * 64,
+                        item.q0[t], item.problem);
+        }
+        for (int j = 0; j < item.n_max && ok; ++j, ++step) {
+          const int stage = step % L::kStages;
+          const uint32_t wrap = (step / L::kStages) & 1;
+          ok = mbar_wait(bar(B::k_empty + stage), wrap ^ 1u, prm.status, 0x0100u | stage);
+          if (!ok) break;
+          mbar_expect_tx(bar(B::k_full + stage), L::kTileBytes);
+#pragma unroll
+          for (int a = 0; a < D / 64; ++a)
+            tma_load_3d(base + L::kKOff + stage * L::kTileBytes + a * L::kAtomBytes, &map_k, bar(B::k_full + stage), a * 64,
+                        j * kTileRows, item.problem);
+          ok = mbar_wait(bar(B::v_empty + stage), wrap ^ 1u, prm.status, 0x0110u | stage);
+          if (!ok) break;
+          mbar_expect_tx(bar(B::v_full + stage), L::kTileBytes);
+#pragma unroll
+          for (int a = 0; a < D / 64; ++a)
+            tma_load_3d(base + L::kVOff + stage * L::kTileBytes + a * L::kAtomBytes, &map_v, bar(B::v_full + stage), a * 64,
+                        j * kTileRows, item.problem);
+        }
       }
     }
   } else if (warp == kMmaWarp) {
     // ================= MMA issuer =================
-    if (lane == 0) {
+    if (lane == 0 && ok) {
       constexpr uint32_t idesc_s = mma_idesc(kTileRows, kTileRows, kFp16, false, false);
       constexpr uint32_t idesc_pv = mma_idesc(kTileRows, D, kFp16, false, true);
       // S_t = Q_t K^T over the head dim, 16 elements per instruction
@@ -217,66 +266,91 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         for (int kk = 4 * part; kk < 4 * part + 4; ++kk)
           mma_ts_lo(c, a + kk * 8, v_lo + kk * (16 * 128 / 16), idesc_pv, (kk > 0 || !first) ? 1u : 0u);
       };
+      unsigned q_uses[kQTiles] = {0u, 0u};  // items finished in which Q tile t had rows
+      unsigned tiles[kQTiles] = {0u, 0u};   // key tiles Q tile t has been through, over all items
+      unsigned step = 0;                    // key tiles consumed so far, over all items
+      for (unsigned n_item = 0; ok; ++n_item) {
+        unsigned index;
+        ok = next_item(n_item, index);
+        if (!ok) break;
+        mbar_arrive(bar(B::work_empty + (n_item & 1u)));
+        if (index >= prm.items) break;
+        const Item item = decode(index);
 #pragma unroll
-      for (int t = 0; t < kQTiles; ++t)
-        if (n_kv[t] > 0 && ok) ok = mbar_wait(bar(B::q_full + t), 0, prm.status, 0x0200u | t);
-      if (ok && n_max > 0) {
-        ok = mbar_wait(bar(B::k_full + 0), 0, prm.status, 0x0210u);
-        if (ok) {
+        for (int t = 0; t < kQTiles; ++t)
+          if (item.n_kv[t] > 0 && ok) ok = mbar_wait(bar(B::q_full + t), q_uses[t] & 1u, prm.status, 0x0200u | t);
+        if (!ok) break;
+        if (item.n_max > 0) {
+          const int stage = step % L::kStages;
+          ok = mbar_wait(bar(B::k_full + stage), (step / L::kStages) & 1, prm.status, 0x0210u);
+          if (!ok) break;
           tc_fence_after_sync();
 #pragma unroll
           for (int t = 0; t < kQTiles; ++t)
-            if (n_kv[t] > 0) {
-              issue_s(t, 0);
+            if (item.n_kv[t] > 0) {
+              // (the S_t region is free: the MMAs run in issue order, and the last one issued for this tile was
+              // the product that consumed the P_t stored there)
+              issue_s(t, stage);
               mma_commit(bar(B::s_full + t));
+              if (item.n_kv[t] == 1) mma_commit(bar(B::q_empty + t));
             }
-          mma_commit(bar(B::k_empty + 0));
+          mma_commit(bar(B::k_empty + stage));
         }
-      }
-      for (int j = 0; j < n_max && ok; ++j) {
-        const int stage = j % L::kStages;
-        const uint32_t wrap = (j / L::kStages) & 1;
-        const int next = (j + 1) % L::kStages;
-        const uint32_t next_wrap = ((j + 1) / L::kStages) & 1;
-        ok = mbar_wait(bar(B::v_full + stage), wrap, prm.status, 0x0220u | stage);
-        bool issued_next = false;
+        for (int j = 0; j < item.n_max && ok; ++j, ++step) {
+          const int stage = step % L::kStages;
+          const uint32_t wrap = (step / L::kStages) & 1;
+          const int next = (step + 1) % L::kStages;
+          const uint32_t next_wrap = ((step + 1) / L::kStages) & 1;
+          ok = mbar_wait(bar(B::v_full + stage), wrap, prm.status, 0x0220u | stage);
+          bool issued_next = false;
 #pragma unroll
-        for (int t = 0; t < kQTiles; ++t) {
-          if (!ok || j >= n_kv[t]) continue;
-          TRACE_EVENT(100 + t);
-          // the product starts on the first 64 keys while the softmax is still on the last 64
-          ok = mbar_wait(bar(B::p_half + t), j & 1, prm.status, 0x0260u | t);
-          if (!ok) break;
-          tc_fence_after_sync();
-          issue_pv(t, stage, 0, j == 0);
-          ok = mbar_wait(bar(B::p_full + t), j & 1, prm.status, 0x0230u | t);
-          if (!ok) break;
-          TRACE_EVENT(110 + t);
-          tc_fence_after_sync();
-          issue_pv(t, stage, 1, j == 0);
-          TRACE_EVENT(120 + t);
-          if (j + 1 < n_kv[t]) {
-            ok = mbar_wait(bar(B::k_full + next), next_wrap, prm.status, 0x0240u | next);
+          for (int t = 0; t < kQTiles; ++t) {
+            if (!ok || j >= item.n_kv[t]) continue;
+            TRACE_EVENT(100 + t);
+            const uint32_t phase = tiles[t] & 1u;
+            // the product starts on the first 64 keys while the softmax is still on the last 64
+            ok = mbar_wait(bar(B::p_half + t), phase, prm.status, 0x0260u | t);
+            if (!ok) break;
+            // the item's first product overwrites O_t: the previous item's epilogue must have read it
+            if (j == 0) ok = mbar_wait(bar(B::o_free + t), (q_uses[t] & 1u) ^ 1u, prm.status, 0x0270u | t);
             if (!ok) break;
             tc_fence_after_sync();
-            issue_s(t, next);
-            mma_commit(bar(B::s_full + t));
-            TRACE_EVENT(130 + t);  // also covers the PV above: O_t is settled when S_t is ready
-            issued_next = true;
-          } else {
-            mma_commit(bar(B::o_full + t));
+            issue_pv(t, stage, 0, j == 0);
+            ok = mbar_wait(bar(B::p_full + t), phase, prm.status, 0x0230u | t);
+            if (!ok) break;
+            TRACE_EVENT(110 + t);
+            tc_fence_after_sync();
+            issue_pv(t, stage, 1, j == 0);
+            TRACE_EVENT(120 + t);
+            ++tiles[t];
+            if (j + 1 < item.n_kv[t]) {
+              // the scores can only follow the product that consumed the P_t lying over them; s_full then also
+              // tells the softmax that O_t is settled
+              ok = mbar_wait(bar(B::k_full + next), next_wrap, prm.status, 0x0240u | next);
+              if (!ok) break;
+              tc_fence_after_sync();
+              issue_s(t, next);
+              mma_commit(bar(B::s_full + t));
+              if (j + 2 == item.n_kv[t]) mma_commit(bar(B::q_empty + t));
+              TRACE_EVENT(130 + t);
+              issued_next = true;
+            } else {
+              mma_commit(bar(B::o_full + t));
+            }
           }
+          if (!ok) break;
+          mma_commit(bar(B::v_empty + stage));
+          if (issued_next) mma_commit(bar(B::k_empty + next));
         }
-        if (!ok) break;
-        mma_commit(bar(B::v_empty + stage));
-        if (issued_next) mma_commit(bar(B::k_empty + next));
+#pragma unroll
+        for (int t = 0; t < kQTiles; ++t)
+          if (item.n_kv[t] > 0) ++q_uses[t];
       }
     }
-  } else {
+  } else if (warp < kProducerWarp) {
     // ================= softmax + epilogue, one thread per query row =================
     const int t = warp >> 2;
     const int row_in_tile = threadIdx.x & 127;
-    const int row = q0[t] + row_in_tile;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_s = tmem + lane_base + L::kSCol + t * 128;
     const uint32_t t_o = tmem + lane_base + L::kOCol + t * D;
@@ -285,13 +359,13 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     // row maximum has outgrown it by more than kRescaleSlack (in log2 units), so most tiles need no
     // rescaling of O_t; until then probabilities may reach 2^kRescaleSlack, which fp32 sums and
     // 16-bit P carry without loss. The result is the same softmax: L = m * scale + log(l).
-    float m = -INFINITY, l = 0.f;
-    const int n = n_kv[t];
     const uint64_t sl2_2 = f2_pack(sl2, sl2);
+    unsigned tiles = 0;   // key tiles this group has been through, over all items
+    unsigned o_uses = 0;  // items this group has finished
     // Key mask: a hidden key is a score of -inf for every row. Each warp keeps its own copy of the tile's 128
     // flags in shared memory as an additive 0 / -inf, each lane fetching four of them one tile ahead of use.
     float* bias = reinterpret_cast<float*>(smem_unaligned + (base - raw) + L::kBiasOff) + warp * 256;
-    auto fetch_flags = [&](int kv0, float (&out4)[4]) {
+    auto fetch_flags = [&](int problem, int kv0, float (&out4)[4]) {
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int key = kv0 + 32 * c + lane;
@@ -299,17 +373,30 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         out4[c] = live ? 0.f : -INFINITY;
       }
     };
+    for (unsigned n_item = 0; ok; ++n_item) {
+    unsigned index;
+    ok = __all_sync(0xffffffffu, next_item(n_item, index));
+    if (!ok) break;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar(B::work_empty + (n_item & 1u)));
+    if (index >= prm.items) break;
+    const Item item = decode(index);
+    const int problem = item.problem;
+    const int n = item.n_kv[t];
+    if (n == 0) continue;
+    const int row = item.q0[t] + row_in_tile;
+    float m = -INFINITY, l = 0.f;
     float flags[4] = {0.f, 0.f, 0.f, 0.f};
-    if (kMask && n > 0) fetch_flags(0, flags);
-    for (int j = 0; j < n; ++j) {
+    if (kMask) fetch_flags(problem, 0, flags);
+    for (int j = 0; j < n; ++j, ++tiles) {
       if (kMask) {
         float* mine = bias + (j & 1) * 128;
 #pragma unroll
         for (int c = 0; c < 4; ++c) mine[32 * c + lane] = flags[c];
         __syncwarp();
-        if (j + 1 < n) fetch_flags((j + 1) * kTileRows, flags);
+        if (j + 1 < n) fetch_flags(problem, (j + 1) * kTileRows, flags);
       }
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full + t), j & 1, prm.status, 0x0300u | t));  // warp-uniform: the tensor-memory ops below are warp-wide
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full + t), tiles & 1u, prm.status, 0x0300u | t));  // warp-uniform: the tensor-memory ops below are warp-wide
       if (!ok) break;
       TRACE_EVENT(2);
       tc_fence_after_sync();
@@ -319,7 +406,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tmem_ld_wait();
       TRACE_EVENT(3);
       const int kv0 = j * kTileRows;
-      const bool diagonal = kCausal && kv0 + kTileRows > q0[t];     // some key of this tile is right of some row
+      const bool diagonal = kCausal && kv0 + kTileRows > item.q0[t];     // some key of this tile is right of some row
       const bool ragged = kv0 + kTileRows > prm.t_k;                // some key of this tile does not exist
       if (diagonal || ragged) {
         int limit = prm.t_k - kv0;                                  // keys [0, limit) of the tile are visible
@@ -418,8 +505,8 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tc_fence_before_sync();
       mbar_arrive(bar(B::p_full + t));
     }
-    if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::o_full + t), 0, prm.status, 0x0310u | t));
-    if (ok && n > 0) {
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::o_full + t), o_uses & 1u, prm.status, 0x0310u | t));
+    if (ok) {
       tc_fence_after_sync();
       const float inv = 1.f / l;
       const long long out_row = static_cast<long long>(problem) * prm.t_q + row;
@@ -444,13 +531,18 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
       }
       if (row < prm.t_q) prm.lse[out_row] = m * prm.scale + logf(l);
+      // O_t is in registers or stored: the next item's first product may overwrite it
+      tc_fence_before_sync();
+      mbar_arrive(bar(B::o_free + t));
+      ++o_uses;
     }
+    }  // items
   }
 
   // ---- teardown ----
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == kMmaWarp) {
+  if (warp == kMmaWarp && !abort_flag) {
     if (*reinterpret_cast<volatile unsigned*>(prm.status) != kStatusOk) {
       // a wait gave up somewhere: give copies and MMAs still in flight time to land before the
       // tensor memory and shared memory they target are released
@@ -458,6 +550,12 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
     tc_fence_after_sync();
     tmem_free(tmem, kTmemCols);
+  }
+  // the last CTA to leave puts the work counters back to zero for the next launch that is handed this pair
+  if (threadIdx.x == 0 && atomicAdd(prm.schedule + 1, 1u) == gridDim.x - 1) {
+    prm.schedule[0] = 0u;
+    prm.schedule[1] = 0u;
+    __threadfence();
   }
 }
 
@@ -483,8 +581,13 @@ int launch_fwd(const Problem& p) {
   prm.trace = reinterpret_cast<long long*>(strtoull(getenv("LIMN_TRACE_PTR"), nullptr, 16));
 #endif
   prm.scale = static_cast<float>(p.scale);
-  const long long ctas = p.bh * prm.q_pairs;
-  if (ctas > 0x7fffffffLL) return fail(LIMN_B200_UNSUPPORTED, "sdpa: %lld CTAs exceed one grid", ctas);
+  const long long items = p.bh * prm.q_pairs;
+  if (items > 0x7fffffffLL) return fail(LIMN_B200_UNSUPPORTED, "sdpa: %lld work items exceed the counter", items);
+  prm.items = static_cast<unsigned>(items);
+  if (int rc = schedule_words(&prm.schedule)) return rc;
+  int sms = 0;
+  if (int rc = sm_count(&sms)) return rc;
+  const long long ctas = items < sms ? items : sms;  // one CTA per SM (shared and tensor memory allow no more), each fetching items until none is left
   auto kernel = sdpa_fwd_kernel<D, kCausal, kFp16, kMask>;
   // the attribute is per device and per kernel instantiation; set it on first use there
   static bool sized[64] = {};

@@ -38,7 +38,8 @@ namespace {
 constexpr long long kMaxRows = 1LL << 20;
 constexpr size_t kStatusBytes = 256;  // the status word, padded so delta starts 256-byte aligned
 
-// [0, 256): status word. [256, 256 + 8 * kMaxRows): delta, float or double per row.
+// [0, 4): status word. [64, 72): the dQ kernel's two work counters. [256, 256 + 8 * kMaxRows): delta, float or
+// double per row.
 // In host code this name is only a handle for cudaGetSymbolAddress; it is not a device address.
 static __device__ __align__(256) unsigned char g_static_scratch[kStatusBytes + 8 * kMaxRows];
 
@@ -86,7 +87,8 @@ extern "C" int limn_b200_sdpa_bwd_q_static(const void* q, const void* k, const v
   unsigned int* status = reinterpret_cast<unsigned int*>(scratch);
   void* delta = scratch + kStatusBytes;
 
-  LIMN_CUDA(cudaMemsetAsync(status, 0, sizeof(unsigned int), s), "clearing the static status word");
+  unsigned int* schedule = reinterpret_cast<unsigned int*>(scratch + 64);
+  LIMN_CUDA(cudaMemsetAsync(scratch, 0, 128, s), "clearing the static status word and work counters");
   int launches = 0;
   if (rows > 0) {
     if (int rc = general_delta(out, dout, delta, dtype, rows, hd_v, s)) return rc;
@@ -98,6 +100,7 @@ extern "C" int limn_b200_sdpa_bwd_q_static(const void* q, const void* k, const v
   p.dtype = dtype, p.bh = bh, p.t_q = t_q, p.t_k = t_k, p.hd = hd, p.hd_v = hd_v;
   p.causal = causal != 0, p.scale = scale, p.stream = s;
   p.status = status;
+  p.schedule = schedule;
   if (int rc = dispatch_op(Op::BwdQ, "sdpa_bwd_q_static", p)) return rc;
   note_launches(launches);
   if (status_out)
