@@ -35,10 +35,10 @@ using namespace ptx;
 
 constexpr int kTileRows = 128;   // query rows per Q tile, keys per K/V tile
 constexpr int kQTiles = 2;       // Q tiles per CTA
-#ifndef LIMN_FWD_THREADS
-#define LIMN_FWD_THREADS 320
-#endif
-constexpr int kThreads = LIMN_FWD_THREADS;
+// Ten warps work; the CTA is launched with twelve because the compiler's register allocation for the softmax
+// loop comes out with far fewer spills at this block size (measured: 3 to 10 % faster). Warps 10 and 11 go
+// straight to the final barrier.
+constexpr int kThreads = 384;
 constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;
 constexpr uint32_t kTmemCols = 512;
