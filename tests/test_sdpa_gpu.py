@@ -197,6 +197,29 @@ def test_two_runs_give_the_same_bits(dev):
             np.testing.assert_array_equal(first.view(np.uint8), second.view(np.uint8))
 
 
+def test_work_counters_come_back_to_zero_launch_after_launch(dev):
+    """The tensor-core kernels' CTAs fetch their work items from a counter pair that the last CTA zeroes again;
+    the pairs are handed out from a ring of 128. More launches than the ring has pairs, with more items than
+    the GPU has SMs (600 > 148) and with fewer, must all give the first launch's bits."""
+    from limn_b200 import host
+
+    for shape in ((150, 2, 200, 64), (3, 1, 300, 128)):
+        q, k, v, do = _random_case(21, BF16, shape, shape, shape)
+        first = None
+        for _ in range(50):  # 3 tensor-core launches per round and shape: 300 in all
+            att = host.Attention(dev, q, k, v, causal=True)
+            out, lse = att.forward()
+            got = (out, lse, *att.backward(do))
+            if first is None:
+                first = got
+                want = oracle.sdpa_forward(q[:1], k[:1], v[:1], causal=True, scale=shape[-1] ** -0.5)[0]
+                assert np.abs(widen(out[:1]) - widen(want)).max() <= 2e-2
+            else:
+                for a, b in zip(first, got, strict=True):
+                    np.testing.assert_array_equal(a.view(np.uint8), b.view(np.uint8))
+        dev.finish()
+
+
 def test_hidden_keys_get_exactly_zero_gradients(dev):
     from limn_b200 import host
 
