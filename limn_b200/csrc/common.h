@@ -60,6 +60,9 @@ int status_word(unsigned int** word);
 // a fixed per-device ring; a pair is only met twice by launches kScheduleRing apart.
 constexpr int kScheduleRing = 128;
 int schedule_words(unsigned int** pair);
+// How many problems the tensor-core kernels schedule as one group (see cta_work): all of them when the GPU
+// has only a few work items per SM, else as many as keep their K and V inside a share of L2.
+int work_group(const Problem& p, long long items, int sms);
 // Streaming multiprocessors of the current device.
 int sm_count(int* count);
 

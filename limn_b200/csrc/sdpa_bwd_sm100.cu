@@ -123,6 +123,7 @@ struct BwdParams {
   void* out1;   // dV
   unsigned* status;
   unsigned* schedule;  // [0] next work item, [1] CTAs that have finished; both zero between launches
+  int group;           // problems per scheduling group (see cta_work)
   unsigned items;      // work items: bh * (tiles of 128 rows a problem's owner side has)
   int t_q, t_k;
   int q_tiles, kv_tiles;
@@ -188,7 +189,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   auto decode = [&](unsigned index) {
     Item item;
     int slot;
-    cta_work(static_cast<int>(index), own_tiles, prm.bh, item.problem, slot);
+    cta_work(static_cast<int>(index), own_tiles, prm.bh, prm.group, item.problem, slot);
     // longest streams first: under causal the last query tile sees every key tile, the first key tile every query tile
     const int own = (kCausal && !kKV) ? own_tiles - 1 - slot : slot;
     item.own0 = own * kTile;
@@ -821,6 +822,7 @@ int launch_bwd(const Problem& p) {
     if (int rc = schedule_words(&prm.schedule)) return rc;
   int sms = 0;
   if (int rc = sm_count(&sms)) return rc;
+  prm.group = work_group(p, items, sms);
   const long long ctas = items < sms ? items : sms;  // one CTA per SM, each fetching items until none is left
   auto kernel = sdpa_bwd_kernel<D, kCausal, kFp16, kKV, kEarly, kSeq, kMask>;
   // the attribute is per device and per kernel instantiation; set it on first use there

@@ -103,6 +103,7 @@ struct FwdParams {
   float* lse;
   unsigned* status;
   unsigned* schedule;  // [0] next work item, [1] CTAs that have finished; both zero between launches
+  int group;           // problems per scheduling group (see cta_work)
   unsigned items;      // work items: bh * q_pairs
   int t_q, t_k;
   int q_pairs;      // work items per problem
@@ -139,7 +140,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   auto decode = [&](unsigned index) {
     Item it;
     int slot;
-    cta_work(static_cast<int>(index), prm.q_pairs, prm.bh, it.problem, slot);
+    cta_work(static_cast<int>(index), prm.q_pairs, prm.bh, prm.group, it.problem, slot);
     const int pair = prm.q_pairs - 1 - slot;  // longest causal rows first
 #pragma unroll
     for (int t = 0; t < kQTiles; ++t) {
@@ -587,6 +588,7 @@ int launch_fwd(const Problem& p) {
   if (int rc = schedule_words(&prm.schedule)) return rc;
   int sms = 0;
   if (int rc = sm_count(&sms)) return rc;
+  prm.group = work_group(p, items, sms);
   const long long ctas = items < sms ? items : sms;  // one CTA per SM (shared and tensor memory allow no more), each fetching items until none is left
   auto kernel = sdpa_fwd_kernel<D, kCausal, kFp16, kMask>;
   // the attribute is per device and per kernel instantiation; set it on first use there

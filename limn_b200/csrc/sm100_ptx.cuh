@@ -344,17 +344,17 @@ __device__ __forceinline__ void exp2_poly2(uint64_t x2, float& lo, float& hi) {
   hi = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
 }
 
-// Which (problem, slot) a CTA takes. CTAs start roughly in index order, so the order is the schedule:
-// problems go in groups of kGroup whose K and V (a few MB) stay in L2 together, and inside a group the
-// slots are walked outermost, all of the group's problems per slot. With `slot 0 = the longest stream`
-// (causal) that is longest-first within a group, and a group ends with its shortest CTAs, which is what
-// keeps the tail of the grid short when a GPU holds only a few groups.
-constexpr int kGroup = 8;
-__device__ __forceinline__ void cta_work(int index, int slots, long long bh, int& problem, int& slot) {
-  const int per_group = kGroup * slots;
+// Which (problem, slot) work item `index` is. Items are fetched in index order, so the order is the schedule:
+// problems go in groups of `group` whose K and V stay in L2 together, and inside a group the slots are walked
+// outermost, all of the group's problems per slot. With `slot 0 = the longest stream` (causal) that is
+// longest-first within a group, and a group ends with its shortest items, which keeps the tail short. The
+// host picks the group as large as L2 allows (work_group below): a GPU that holds only a few dozen
+// problems then runs them as one group, longest items of all problems first.
+__device__ __forceinline__ void cta_work(int index, int slots, long long bh, int group_size, int& problem, int& slot) {
+  const int per_group = group_size * slots;
   const int group = index / per_group;
-  const int first = group * kGroup;
-  const int members = static_cast<int>(bh - first < kGroup ? bh - first : kGroup);
+  const int first = group * group_size;
+  const int members = static_cast<int>(bh - first < group_size ? bh - first : group_size);
   const int within = index - group * per_group;
   slot = within / members;
   problem = first + within - slot * members;
