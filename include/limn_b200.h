@@ -92,6 +92,39 @@ int limn_b200_sdpa_bwd_q_static(const void* q, const void* k, const void* v, con
 int limn_b200_sdpa_delta(const void* out, const void* dout, void* delta,
                          int dtype, long long rows, int hd_v, void* stream);
 
+/* ---- operands as the model holds them: (batch, t, heads, hd) ----
+ * limn's frontend permutes (batch, t, heads, hd) activations to (batch, heads, t, hd) and wraps each operand in
+ * CONTIGUOUS before the CUSTOM node (limn/tensor.py:561-562; the gradient of that permute copies again on the way
+ * back, limn/tensor.py:736-746), so every attention call is surrounded by full-tensor copies. These entry points
+ * read and write the token-major layout in place through the tensor maps' strides, so a frontend that skips the
+ * permute can skip the copies too. They have no counterpart in the reference.
+ *   layout LIMN_B200_BHTD: q, k, v, dout, out, dq, dk, dv are (batch, heads, t, hd) dense: the same as the entry
+ *     points above with bh = batch * heads.
+ *   layout LIMN_B200_BTHD: they are (batch, t, heads, hd) dense.
+ *   Either way lse and delta are (batch * heads, t_q) and key_mask (batch * heads, t_k), as above.
+ *   LIMN_B200_BTHD is served for f16/bf16 with hd == hd_v in {64, 128} (the tensor-core kernels); anything else
+ *   returns LIMN_B200_UNSUPPORTED and launches nothing. */
+enum limn_b200_layout {
+  LIMN_B200_BHTD = 0,
+  LIMN_B200_BTHD = 1
+};
+int limn_b200_sdpa_fwd_layout(const void* q, const void* k, const void* v, const void* key_mask,
+                              void* out, void* lse,
+                              int layout, int dtype, int batch, int heads, int t_q, int t_k, int hd, int hd_v,
+                              int causal, double scale, void* stream);
+int limn_b200_sdpa_bwd_q_layout(const void* q, const void* k, const void* v, const void* dout,
+                                const void* lse, const void* delta, const void* key_mask,
+                                void* dq,
+                                int layout, int dtype, int batch, int heads, int t_q, int t_k, int hd, int hd_v,
+                                int causal, double scale, void* stream);
+int limn_b200_sdpa_bwd_kv_layout(const void* q, const void* k, const void* v, const void* dout,
+                                 const void* lse, const void* delta, const void* key_mask,
+                                 void* dk, void* dv,
+                                 int layout, int dtype, int batch, int heads, int t_q, int t_k, int hd, int hd_v,
+                                 int causal, double scale, void* stream);
+int limn_b200_sdpa_delta_layout(const void* out, const void* dout, void* delta,
+                                int layout, int dtype, int batch, int heads, int t_q, int hd_v, void* stream);
+
 /* Which path the dispatcher picks for a problem (a limn_b200_path value), or -1 with an
  * error message if the arguments are invalid. Launches nothing. */
 int limn_b200_sdpa_path(int dtype, long long bh, int t_q, int t_k, int hd, int hd_v,

@@ -21,12 +21,19 @@ PATH_GENERAL, PATH_TCGEN05 = 0, 1
 _P = c_void_p
 _SHAPE = (c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_double, _P)  # dtype, bh, t_q, t_k, hd, hd_v, causal, scale, stream
 
+# layout, dtype, batch, heads, t_q, t_k, hd, hd_v, causal, scale, stream
+_LAYOUT_SHAPE = (c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_double, _P)
+LAYOUT_CODES = {"bhtd": 0, "bthd": 1}
 SIGNATURES = {
     "limn_b200_sdpa_fwd": (c_int, (_P, _P, _P, _P, _P, _P) + _SHAPE),
     "limn_b200_sdpa_bwd_q": (c_int, (_P, _P, _P, _P, _P, _P, _P, _P) + _SHAPE),
     "limn_b200_sdpa_bwd_kv": (c_int, (_P, _P, _P, _P, _P, _P, _P, _P, _P) + _SHAPE),
     "limn_b200_sdpa_bwd_q_static": (c_int, (_P, _P, _P, _P, _P, _P, _P, _P, _P) + _SHAPE),
     "limn_b200_sdpa_delta": (c_int, (_P, _P, _P, c_int, c_longlong, c_int, _P)),
+    "limn_b200_sdpa_fwd_layout": (c_int, (_P, _P, _P, _P, _P, _P) + _LAYOUT_SHAPE),
+    "limn_b200_sdpa_bwd_q_layout": (c_int, (_P, _P, _P, _P, _P, _P, _P, _P) + _LAYOUT_SHAPE),
+    "limn_b200_sdpa_bwd_kv_layout": (c_int, (_P, _P, _P, _P, _P, _P, _P, _P, _P) + _LAYOUT_SHAPE),
+    "limn_b200_sdpa_delta_layout": (c_int, (_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P)),
     "limn_b200_sdpa_path": (c_int, (c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_double)),
     "limn_b200_last_launch_count": (c_int, ()),
     "limn_b200_last_error": (c_char_p, ()),

@@ -105,7 +105,14 @@ int sm_count(int* count) {
   return LIMN_B200_OK;
 }
 
-int make_tile_map(CUtensorMap* map, const void* base, bool fp16, long long bh, int rows, int width, int box_rows) {
+Strides strides_of(int layout, int heads, int rows, int width) {
+  if (layout == LIMN_B200_BTHD)
+    return Strides{static_cast<long long>(rows) * heads * width, width, static_cast<long long>(heads) * width};
+  return Strides{static_cast<long long>(heads) * rows * width, static_cast<long long>(rows) * width, width};
+}
+
+int make_tile_map(CUtensorMap* map, const void* base, bool fp16, int batch, int heads, int rows, int width, int box_rows,
+                  const Strides& strides) {
   std::call_once(g_encode_once, [] {
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult found;
@@ -117,13 +124,16 @@ int make_tile_map(CUtensorMap* map, const void* base, bool fp16, long long bh, i
     return fail(LIMN_B200_CUDA_ERROR, "cuda: the driver does not export cuTensorMapEncodeTiled");
   if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0)
     return fail(LIMN_B200_BAD_ARGUMENT, "sdpa: tensor base %p is not 16-byte aligned", base);
-  // A map depends only on the base address and the extents, and a host that pools its buffers (limn does,
-  // limn/backend_cuda.py:297-307) hands the same ones back step after step, so the last few encodings are kept
-  // per thread. At the smallest shapes the encoding costs as much host time as the kernel takes to run.
+  if ((strides.batch | strides.head | strides.row) & 7)
+    return fail(LIMN_B200_BAD_ARGUMENT, "sdpa: operand strides must be multiples of 8 elements");
+  // A map depends only on the base address, the extents and the strides, and a host that pools its buffers
+  // (limn does, limn/backend_cuda.py:297-307) hands the same ones back step after step, so the last few
+  // encodings are kept per thread. At the smallest shapes the encoding costs as much host time as the kernel
+  // takes to run.
   struct Entry {
     const void* base;
-    long long bh;
-    int rows, width, box_rows, fp16;
+    int batch, heads, rows, width, box_rows, fp16;
+    Strides strides;
     CUtensorMap map;
   };
   constexpr int kEntries = 16;
@@ -131,22 +141,26 @@ int make_tile_map(CUtensorMap* map, const void* base, bool fp16, long long bh, i
   thread_local int used = 0, next_slot = 0;
   for (int i = 0; i < used; ++i) {
     const Entry& e = cache[i];
-    if (e.base == base && e.bh == bh && e.rows == rows && e.width == width && e.box_rows == box_rows && e.fp16 == (fp16 ? 1 : 0)) {
+    if (e.base == base && e.batch == batch && e.heads == heads && e.rows == rows && e.width == width &&
+        e.box_rows == box_rows && e.fp16 == (fp16 ? 1 : 0) && e.strides.batch == strides.batch &&
+        e.strides.head == strides.head && e.strides.row == strides.row) {
       *map = e.map;
       return LIMN_B200_OK;
     }
   }
-  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(width), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(bh)};
-  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(width) * 2, static_cast<cuuint64_t>(rows) * width * 2};
-  const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
-  const cuuint32_t elem[3] = {1, 1, 1};
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(width), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(heads),
+                              static_cast<cuuint64_t>(batch)};
+  const cuuint64_t byte_strides[3] = {static_cast<cuuint64_t>(strides.row) * 2, static_cast<cuuint64_t>(strides.head) * 2,
+                                      static_cast<cuuint64_t>(strides.batch) * 2};
+  const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
+  const cuuint32_t elem[4] = {1, 1, 1, 1};
   const CUresult res = g_encode_tiled(
-      map, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims,
-      strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+      map, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims,
+      byte_strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (res != CUDA_SUCCESS) return fail(LIMN_B200_CUDA_ERROR, "cuda: encoding a tensor map failed with CUresult %d", (int)res);
   Entry& slot = cache[next_slot];
-  slot = Entry{base, bh, rows, width, box_rows, fp16 ? 1 : 0, *map};
+  slot = Entry{base, batch, heads, rows, width, box_rows, fp16 ? 1 : 0, strides, *map};
   next_slot = (next_slot + 1) % kEntries;
   if (used < kEntries) ++used;
   return LIMN_B200_OK;
@@ -191,6 +205,11 @@ int dispatch_op(Op op, const char* name, const Problem& p) {
   if (!have_inputs || !have_rest) return fail(LIMN_B200_BAD_ARGUMENT, "%s: a required pointer is null", name);
   if (p.bh == 0) return LIMN_B200_OK;
   if (tcgen05_serves(op, p)) return tcgen05_launch(op, p);
+  if (p.layout != LIMN_B200_BHTD)
+    return fail(LIMN_B200_UNSUPPORTED,
+                "%s: the (batch, t, heads, hd) layout is served for f16/bf16 with hd == hd_v in {64, 128}; make the "
+                "operands contiguous as (batch, heads, t, hd) for anything else",
+                name);
   return general_launch(op, p);
 }
 
@@ -222,6 +241,68 @@ int limn_b200_sdpa_bwd_kv(const void* q, const void* k, const void* v, const voi
   Problem p = problem(q, k, v, key_mask, dtype, bh, t_q, t_k, hd, hd_v, causal, scale, stream);
   p.dout = dout, p.lse_in = lse, p.delta = delta, p.dk = dk, p.dv = dv;
   return dispatch_op(Op::BwdKV, "sdpa_bwd_kv", p);
+}
+
+namespace {
+
+// The layout entry points' shared argument handling: bh = batch * heads, heads kept for the strides.
+int with_layout(const char* name, Problem& p, int layout, int batch, int heads) {
+  if (layout != LIMN_B200_BHTD && layout != LIMN_B200_BTHD)
+    return fail(LIMN_B200_BAD_ARGUMENT, "%s: unknown layout code %d", name, layout);
+  if (batch < 0 || heads <= 0) return fail(LIMN_B200_BAD_ARGUMENT, "%s: batch must be >= 0 and heads > 0", name);
+  p.bh = static_cast<long long>(batch) * heads;
+  p.layout = layout;
+  p.heads = layout == LIMN_B200_BHTD ? 0 : heads;  // dense operands are bh problems of one "batch"
+  return LIMN_B200_OK;
+}
+
+}  // namespace
+
+int limn_b200_sdpa_fwd_layout(const void* q, const void* k, const void* v, const void* key_mask, void* out, void* lse,
+                              int layout, int dtype, int batch, int heads, int t_q, int t_k, int hd, int hd_v,
+                              int causal, double scale, void* stream) {
+  clear_error();
+  Problem p = problem(q, k, v, key_mask, dtype, 0, t_q, t_k, hd, hd_v, causal, scale, stream);
+  if (int rc = with_layout("sdpa", p, layout, batch, heads)) return rc;
+  p.out = out, p.lse_out = lse;
+  return dispatch_op(Op::Fwd, "sdpa", p);
+}
+
+int limn_b200_sdpa_bwd_q_layout(const void* q, const void* k, const void* v, const void* dout, const void* lse,
+                                const void* delta, const void* key_mask, void* dq, int layout, int dtype, int batch,
+                                int heads, int t_q, int t_k, int hd, int hd_v, int causal, double scale, void* stream) {
+  clear_error();
+  Problem p = problem(q, k, v, key_mask, dtype, 0, t_q, t_k, hd, hd_v, causal, scale, stream);
+  if (int rc = with_layout("sdpa_bwd_q", p, layout, batch, heads)) return rc;
+  p.dout = dout, p.lse_in = lse, p.delta = delta, p.dq = dq;
+  return dispatch_op(Op::BwdQ, "sdpa_bwd_q", p);
+}
+
+int limn_b200_sdpa_bwd_kv_layout(const void* q, const void* k, const void* v, const void* dout, const void* lse,
+                                 const void* delta, const void* key_mask, void* dk, void* dv, int layout, int dtype,
+                                 int batch, int heads, int t_q, int t_k, int hd, int hd_v, int causal, double scale,
+                                 void* stream) {
+  clear_error();
+  Problem p = problem(q, k, v, key_mask, dtype, 0, t_q, t_k, hd, hd_v, causal, scale, stream);
+  if (int rc = with_layout("sdpa_bwd_kv", p, layout, batch, heads)) return rc;
+  p.dout = dout, p.lse_in = lse, p.delta = delta, p.dk = dk, p.dv = dv;
+  return dispatch_op(Op::BwdKV, "sdpa_bwd_kv", p);
+}
+
+int limn_b200_sdpa_delta_layout(const void* out, const void* dout, void* delta, int layout, int dtype, int batch,
+                                int heads, int t_q, int hd_v, void* stream) {
+  clear_error();
+  g_launches = 0;
+  if (!out || !dout || !delta) return fail(LIMN_B200_BAD_ARGUMENT, "sdpa_delta: a required pointer is null");
+  if (layout != LIMN_B200_BHTD && layout != LIMN_B200_BTHD)
+    return fail(LIMN_B200_BAD_ARGUMENT, "sdpa_delta: unknown layout code %d", layout);
+  if (batch < 0 || heads <= 0 || t_q <= 0 || hd_v <= 0)
+    return fail(LIMN_B200_BAD_ARGUMENT, "sdpa_delta: extents must be positive");
+  if (batch == 0) return LIMN_B200_OK;
+  if (layout == LIMN_B200_BHTD)
+    return general_delta(out, dout, delta, dtype, static_cast<long long>(batch) * heads * t_q, hd_v,
+                         static_cast<cudaStream_t>(stream));
+  return general_delta_bthd(out, dout, delta, dtype, batch, heads, t_q, hd_v, static_cast<cudaStream_t>(stream));
 }
 
 int limn_b200_sdpa_delta(const void* out, const void* dout, void* delta, int dtype, long long rows, int hd_v,

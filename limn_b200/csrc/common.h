@@ -31,6 +31,10 @@ struct Problem {
   int causal = 0;
   double scale = 0.0;
   cudaStream_t stream = nullptr;
+  // Operand layout (a limn_b200_layout value). Dense (BHTD) problems leave heads at 0: bh problems, one "batch".
+  // With heads > 0, bh = batch * heads and problem p is (batch p / heads, head p % heads).
+  int layout = 0;
+  int heads = 0;
   // Where kernels that wait record giving up. Null means the per-device word status_word() allocates.
   unsigned int* status = nullptr;
   // Two zeroed words for the kernels' work counters. Null means a pair from schedule_words().
@@ -73,6 +77,8 @@ int dispatch_op(Op op, const char* name, const Problem& p);
 int general_launch(Op op, const Problem& p);
 int general_delta(const void* out, const void* dout, void* delta, int dtype, long long rows, int hd_v,
                   cudaStream_t stream);
+int general_delta_bthd(const void* out, const void* dout, void* delta, int dtype, int batch, int heads, int t, int hd_v,
+                       cudaStream_t stream);
 bool tcgen05_serves(Op op, const Problem& p);
 int tcgen05_launch(Op op, const Problem& p);
 

@@ -124,6 +124,8 @@ struct BwdParams {
   unsigned* status;
   unsigned* schedule;  // [0] next work item, [1] CTAs that have finished; both zero between launches
   int group;           // problems per scheduling group (see cta_work)
+  int heads;           // problem p is (batch p / heads, head p % heads) in the tensor maps and in the outputs
+  Strides out_strides; // of dQ (dQ pass) or of dK and dV (dK/dV pass), in elements
   unsigned items;      // work items: bh * (tiles of 128 rows a problem's owner side has)
   int t_q, t_k;
   int q_tiles, kv_tiles;
@@ -182,6 +184,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const int own_tiles = kKV ? prm.kv_tiles : prm.q_tiles;
   struct Item {
     int problem;
+    int head, batch;  // the problem's coordinates in the operands
     int own0;    // first owned row
     int first;   // first streamed tile
     int count;   // streamed tiles
@@ -190,6 +193,8 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     Item item;
     int slot;
     cta_work(static_cast<int>(index), own_tiles, prm.bh, prm.group, item.problem, slot);
+    item.batch = item.problem / prm.heads;
+    item.head = item.problem - item.batch * prm.heads;
     // longest streams first: under causal the last query tile sees every key tile, the first key tile every query tile
     const int own = (kCausal && !kKV) ? own_tiles - 1 - slot : slot;
     item.own0 = own * kTile;
@@ -286,8 +291,8 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         mbar_expect_tx(bar(B::held_full), 2 * L::kTileBytes);
 #pragma unroll
         for (int a = 0; a < D / 64; ++a) {
-          tma_load_3d(held_a_smem + a * L::kAtomBytes, held_a, bar(B::held_full), a * 64, item.own0, item.problem);
-          tma_load_3d(held_b_smem + a * L::kAtomBytes, held_b, bar(B::held_full), a * 64, item.own0, item.problem);
+          tma_load_4d(held_a_smem + a * L::kAtomBytes, held_a, bar(B::held_full), a * 64, item.own0, item.head, item.batch);
+          tma_load_4d(held_b_smem + a * L::kAtomBytes, held_b, bar(B::held_full), a * 64, item.own0, item.head, item.batch);
         }
         for (int it = 0; it < item.count; ++it) {
           const int g = done + it;
@@ -297,13 +302,13 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           mbar_expect_tx(a_full(g), L::kTileBytes);
 #pragma unroll
           for (int a = 0; a < D / 64; ++a)
-            tma_load_3d(stream_a_smem(g) + a * L::kAtomBytes, stream_a, a_full(g), a * 64, row0, item.problem);
+            tma_load_4d(stream_a_smem(g) + a * L::kAtomBytes, stream_a, a_full(g), a * 64, row0, item.head, item.batch);
           ok = mbar_wait(b_empty(g), b_wrap(g) ^ 1u, prm.status, 0x1110u);
           if (!ok) break;
           mbar_expect_tx(b_full(g), L::kTileBytes);
 #pragma unroll
           for (int a = 0; a < D / 64; ++a)
-            tma_load_3d(stream_b_smem(g) + a * L::kAtomBytes, stream_b, b_full(g), a * 64, row0, item.problem);
+            tma_load_4d(stream_b_smem(g) + a * L::kAtomBytes, stream_b, b_full(g), a * 64, row0, item.head, item.batch);
         }
         done += item.count;
       }
@@ -736,7 +741,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       if (kKV) {
         // group 0 writes this key's dV row, group 1 its dK row
         const bool in = row < prm.t_k;
-        const long long out_row = static_cast<long long>(problem) * prm.t_k + row;
+        const long long out_at = item.batch * prm.out_strides.batch + item.head * prm.out_strides.head + row * prm.out_strides.row;
         const uint32_t t_acc = tmem + lane_base + (group == 0 ? L::kAcc0 : L::kAcc1);
         void* dst = group == 0 ? prm.out1 : prm.out0;
         const float mul = group == 0 ? 1.f : prm.scale;
@@ -745,19 +750,19 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           uint32_t acc[32];
           tmem_ld32(t_acc + 32 * c, acc);
           tmem_ld_wait();
-          if (in) store_row32<kFp16>(dst, out_row * D + 32 * c, acc, mul);
+          if (in) store_row32<kFp16>(dst, out_at + 32 * c, acc, mul);
         }
       } else {
         // each group writes half of this query's dQ row
         const bool in = row < prm.t_q;
-        const long long out_row = static_cast<long long>(problem) * prm.t_q + row;
+        const long long out_at = item.batch * prm.out_strides.batch + item.head * prm.out_strides.head + row * prm.out_strides.row;
 #pragma unroll
         for (int c = 0; c < D / 64; ++c) {
           const int col = group * (D / 2) + 32 * c;
           uint32_t acc[32];
           tmem_ld32(tmem + lane_base + L::kAcc0 + col, acc);
           tmem_ld_wait();
-          if (in) store_row32<kFp16>(prm.out0, out_row * D + col, acc, prm.scale);
+          if (in) store_row32<kFp16>(prm.out0, out_at + col, acc, prm.scale);
         }
       }
       // the accumulators are in registers or stored: the next item's first products may overwrite them
@@ -793,16 +798,20 @@ int launch_bwd(const Problem& p) {
   constexpr bool kSeq = !kEarly;            // ... so there S^T and dP^T share one region, one after the other
   using L = BwdLayout<D, kKV, kMask>;
   CUtensorMap map_q, map_k, map_v, map_do;
-  if (int rc = make_tile_map(&map_q, p.q, kFp16, p.bh, p.t_q, D, kTile)) return rc;
-  if (int rc = make_tile_map(&map_k, p.k, kFp16, p.bh, p.t_k, D, kTile)) return rc;
-  if (int rc = make_tile_map(&map_v, p.v, kFp16, p.bh, p.t_k, D, kTile)) return rc;
-  if (int rc = make_tile_map(&map_do, p.dout, kFp16, p.bh, p.t_q, D, kTile)) return rc;
+  const int heads = p.heads > 0 ? p.heads : static_cast<int>(p.bh), batch = static_cast<int>(p.bh / heads);
+  const Strides of_q = strides_of(p.layout, heads, p.t_q, D), of_k = strides_of(p.layout, heads, p.t_k, D);
+  if (int rc = make_tile_map(&map_q, p.q, kFp16, batch, heads, p.t_q, D, kTile, of_q)) return rc;
+  if (int rc = make_tile_map(&map_k, p.k, kFp16, batch, heads, p.t_k, D, kTile, of_k)) return rc;
+  if (int rc = make_tile_map(&map_v, p.v, kFp16, batch, heads, p.t_k, D, kTile, of_k)) return rc;
+  if (int rc = make_tile_map(&map_do, p.dout, kFp16, batch, heads, p.t_q, D, kTile, of_q)) return rc;
   BwdParams prm;
   prm.mask = static_cast<const unsigned short*>(p.mask);
   prm.lse = static_cast<const float*>(p.lse_in);
   prm.delta = static_cast<const float*>(p.delta);
   prm.out0 = kKV ? p.dk : p.dq;
   prm.out1 = kKV ? p.dv : nullptr;
+  prm.heads = heads;
+  prm.out_strides = kKV ? of_k : of_q;
   prm.status = p.status;
   if (prm.status == nullptr)
     if (int rc = status_word(&prm.status)) return rc;

@@ -104,6 +104,8 @@ struct FwdParams {
   unsigned* status;
   unsigned* schedule;  // [0] next work item, [1] CTAs that have finished; both zero between launches
   int group;           // problems per scheduling group (see cta_work)
+  int heads;           // problem p is (batch p / heads, head p % heads) in the tensor maps and in `out`
+  Strides out_strides; // of O, in elements
   unsigned items;      // work items: bh * q_pairs
   int t_q, t_k;
   int q_pairs;      // work items per problem
@@ -133,6 +135,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   // ---- which rows a work item covers ----
   struct Item {
     int problem;
+    int head, batch;    // the problem's coordinates in the operands
     int q0[kQTiles];    // first query row of each Q tile
     int n_kv[kQTiles];  // key tiles each Q tile consumes
     int n_max;
@@ -141,6 +144,8 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     Item it;
     int slot;
     cta_work(static_cast<int>(index), prm.q_pairs, prm.bh, prm.group, it.problem, slot);
+    it.batch = it.problem / prm.heads;
+    it.head = it.problem - it.batch * prm.heads;
     const int pair = prm.q_pairs - 1 - slot;  // longest causal rows first
 #pragma unroll
     for (int t = 0; t < kQTiles; ++t) {
@@ -217,8 +222,8 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           mbar_expect_tx(bar(B::q_full + t), L::kTileBytes);
 #pragma unroll
           for (int a = 0; a < D / 64; ++a)
-            tma_load_3d(base + L::kQOff + t * L::kTileBytes + a * L::kAtomBytes, &map_q, bar(B::q_full + t), a * 64,
-                        item.q0[t], item.problem);
+            tma_load_4d(base + L::kQOff + t * L::kTileBytes + a * L::kAtomBytes, &map_q, bar(B::q_full + t), a * 64,
+                        item.q0[t], item.head, item.batch);
         }
         for (int j = 0; j < item.n_max && ok; ++j, ++step) {
           const int stage = step % L::kStages;
@@ -228,15 +233,15 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           mbar_expect_tx(bar(B::k_full + stage), L::kTileBytes);
 #pragma unroll
           for (int a = 0; a < D / 64; ++a)
-            tma_load_3d(base + L::kKOff + stage * L::kTileBytes + a * L::kAtomBytes, &map_k, bar(B::k_full + stage), a * 64,
-                        j * kTileRows, item.problem);
+            tma_load_4d(base + L::kKOff + stage * L::kTileBytes + a * L::kAtomBytes, &map_k, bar(B::k_full + stage), a * 64,
+                        j * kTileRows, item.head, item.batch);
           ok = mbar_wait(bar(B::v_empty + stage), wrap ^ 1u, prm.status, 0x0110u | stage);
           if (!ok) break;
           mbar_expect_tx(bar(B::v_full + stage), L::kTileBytes);
 #pragma unroll
           for (int a = 0; a < D / 64; ++a)
-            tma_load_3d(base + L::kVOff + stage * L::kTileBytes + a * L::kAtomBytes, &map_v, bar(B::v_full + stage), a * 64,
-                        j * kTileRows, item.problem);
+            tma_load_4d(base + L::kVOff + stage * L::kTileBytes + a * L::kAtomBytes, &map_v, bar(B::v_full + stage), a * 64,
+                        j * kTileRows, item.head, item.batch);
         }
       }
     }
@@ -510,14 +515,15 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     if (ok) {
       tc_fence_after_sync();
       const float inv = 1.f / l;
-      const long long out_row = static_cast<long long>(problem) * prm.t_q + row;
+      const long long out_row = static_cast<long long>(problem) * prm.t_q + row;  // in L, which is always dense
+      const long long out_at = item.batch * prm.out_strides.batch + item.head * prm.out_strides.head + row * prm.out_strides.row;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t o[32];
         tmem_ld32(t_o + 32 * c, o);
         tmem_ld_wait();
         if (row < prm.t_q) {
-          uint4* dst = reinterpret_cast<uint4*>(static_cast<unsigned char*>(prm.out) + (out_row * D + 32 * c) * 2);
+          uint4* dst = reinterpret_cast<uint4*>(static_cast<unsigned char*>(prm.out) + (out_at + 32 * c) * 2);
 #pragma unroll
           for (int v4 = 0; v4 < 4; ++v4) {
             uint32_t w[4];
@@ -564,11 +570,15 @@ template <int D, bool kCausal, bool kFp16, bool kMask>
 int launch_fwd(const Problem& p) {
   using L = FwdLayout<D>;
   CUtensorMap map_q, map_k, map_v;
-  if (int rc = make_tile_map(&map_q, p.q, kFp16, p.bh, p.t_q, D, kTileRows)) return rc;
-  if (int rc = make_tile_map(&map_k, p.k, kFp16, p.bh, p.t_k, D, kTileRows)) return rc;
-  if (int rc = make_tile_map(&map_v, p.v, kFp16, p.bh, p.t_k, D, kTileRows)) return rc;
+  const int heads = p.heads > 0 ? p.heads : static_cast<int>(p.bh), batch = static_cast<int>(p.bh / heads);
+  const Strides of_q = strides_of(p.layout, heads, p.t_q, D), of_k = strides_of(p.layout, heads, p.t_k, D);
+  if (int rc = make_tile_map(&map_q, p.q, kFp16, batch, heads, p.t_q, D, kTileRows, of_q)) return rc;
+  if (int rc = make_tile_map(&map_k, p.k, kFp16, batch, heads, p.t_k, D, kTileRows, of_k)) return rc;
+  if (int rc = make_tile_map(&map_v, p.v, kFp16, batch, heads, p.t_k, D, kTileRows, of_k)) return rc;
   FwdParams prm;
   prm.out = p.out;
+  prm.heads = heads;
+  prm.out_strides = of_q;
   prm.mask = static_cast<const unsigned short*>(p.mask);
   prm.lse = static_cast<float*>(p.lse_out);
   prm.status = p.status;

@@ -289,7 +289,7 @@ row_dot_kernel(const T* __restrict__ out, const T* __restrict__ dout, C* __restr
 template <bool kFp16, int kLanes>
 __global__ void __launch_bounds__(256)
 row_dot16_kernel(const uint4* __restrict__ out, const uint4* __restrict__ dout, float* __restrict__ delta,
-                 long long rows) {
+                 long long rows, int heads, int t) {
   const long long piece = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;  // 16-byte piece index
   const long long row = piece / kLanes;
   float acc = 0.f;
@@ -313,11 +313,22 @@ row_dot16_kernel(const uint4* __restrict__ out, const uint4* __restrict__ dout, 
   }
 #pragma unroll
   for (int off = kLanes / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(kFull, acc, off);
-  if (row < rows && (threadIdx.x & (kLanes - 1)) == 0) delta[row] = acc;
+  if (row < rows && (threadIdx.x & (kLanes - 1)) == 0) {
+    long long to = row;
+    if (heads > 0) {
+      // rows lie in memory as (batch, t, head); delta is (batch, head, t)
+      const long long bt = row / heads;
+      const int h = static_cast<int>(row - bt * heads);
+      const long long b = bt / t;
+      to = (b * heads + h) * t + (bt - b * t);
+    }
+    delta[to] = acc;
+  }
 }
 
 template <bool kFp16>
-bool launch_row_dot16(const void* out, const void* dout, void* delta, long long rows, int hd_v, cudaStream_t stream) {
+bool launch_row_dot16(const void* out, const void* dout, void* delta, long long rows, int hd_v, cudaStream_t stream,
+                      int heads = 0, int t = 0) {
   const int lanes = hd_v / 8;
   if (hd_v % 8 != 0 || lanes > 32 || (lanes & (lanes - 1)) != 0) return false;
   if ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(dout)) & 15u) return false;
@@ -328,12 +339,12 @@ bool launch_row_dot16(const void* out, const void* dout, void* delta, long long 
   auto a = static_cast<const uint4*>(out), b = static_cast<const uint4*>(dout);
   auto d = static_cast<float*>(delta);
   switch (lanes) {
-    case 1: row_dot16_kernel<kFp16, 1><<<grid, block, 0, stream>>>(a, b, d, rows); break;
-    case 2: row_dot16_kernel<kFp16, 2><<<grid, block, 0, stream>>>(a, b, d, rows); break;
-    case 4: row_dot16_kernel<kFp16, 4><<<grid, block, 0, stream>>>(a, b, d, rows); break;
-    case 8: row_dot16_kernel<kFp16, 8><<<grid, block, 0, stream>>>(a, b, d, rows); break;
-    case 16: row_dot16_kernel<kFp16, 16><<<grid, block, 0, stream>>>(a, b, d, rows); break;
-    default: row_dot16_kernel<kFp16, 32><<<grid, block, 0, stream>>>(a, b, d, rows); break;
+    case 1: row_dot16_kernel<kFp16, 1><<<grid, block, 0, stream>>>(a, b, d, rows, heads, t); break;
+    case 2: row_dot16_kernel<kFp16, 2><<<grid, block, 0, stream>>>(a, b, d, rows, heads, t); break;
+    case 4: row_dot16_kernel<kFp16, 4><<<grid, block, 0, stream>>>(a, b, d, rows, heads, t); break;
+    case 8: row_dot16_kernel<kFp16, 8><<<grid, block, 0, stream>>>(a, b, d, rows, heads, t); break;
+    case 16: row_dot16_kernel<kFp16, 16><<<grid, block, 0, stream>>>(a, b, d, rows, heads, t); break;
+    default: row_dot16_kernel<kFp16, 32><<<grid, block, 0, stream>>>(a, b, d, rows, heads, t); break;
   }
   return true;
 }
@@ -434,6 +445,18 @@ int general_delta(const void* out, const void* dout, void* delta, int dtype, lon
   LIMN_CUDA(cudaGetLastError(), "launching the row-dot kernel");
   note_launches(1);
   return LIMN_B200_OK;
+}
+
+int general_delta_bthd(const void* out, const void* dout, void* delta, int dtype, int batch, int heads, int t, int hd_v,
+                       cudaStream_t stream) {
+  const long long rows = static_cast<long long>(batch) * heads * t;
+  if ((dtype == LIMN_B200_F16 && launch_row_dot16<true>(out, dout, delta, rows, hd_v, stream, heads, t)) ||
+      (dtype == LIMN_B200_BF16 && launch_row_dot16<false>(out, dout, delta, rows, hd_v, stream, heads, t))) {
+    LIMN_CUDA(cudaGetLastError(), "launching the row-dot kernel");
+    note_launches(1);
+    return LIMN_B200_OK;
+  }
+  return fail(LIMN_B200_UNSUPPORTED, "sdpa_delta: the (batch, t, heads, hd) layout is served for f16/bf16 with hd_v a power of two from 8 to 256");
 }
 
 }  // namespace limn_b200

@@ -47,6 +47,13 @@ def test_argument_checks_answer_without_a_device():
     assert lib().limn_b200_sdpa_bwd_kv(one, one, one, one, one, one, None, one, None, 0, 1, 4, 4, 8, 8, 0, 1.0, None) == 1
     # an empty batch is a successful no-op
     assert fwd(one, one, one, None, one, one, 0, 0, 4, 4, 8, 8, 0, 1.0, None) == 0 and err() == ""
+    # the layout entry points check their own arguments first, then the same ones
+    laid = lib().limn_b200_sdpa_fwd_layout
+    assert laid(one, one, one, None, one, one, 7, 2, 1, 2, 4, 4, 64, 64, 0, 1.0, None) == 1 and "layout" in err()
+    assert laid(one, one, one, None, one, one, 1, 2, 1, 0, 4, 4, 64, 64, 0, 1.0, None) == 1 and "heads" in err()
+    assert laid(one, one, one, None, one, one, 1, 2, 1, 2, 4, 5, 64, 64, 1, 1.0, None) == 1 and "square keys" in err()
+    assert laid(one, one, one, None, one, one, 1, 2, 0, 2, 4, 4, 64, 64, 0, 1.0, None) == 0 and err() == ""
+    assert lib().limn_b200_sdpa_delta_layout(one, one, one, 5, 2, 1, 2, 4, 64, None) == 1 and "layout" in err()
 
 
 def test_dispatch_policy():
