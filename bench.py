@@ -253,6 +253,9 @@ class Shard:
             self.grad_host = [torch.empty(shape, dtype=torch.int16).pin_memory() for _ in range(3)]
         self.launches = 0
         self.pipeline = None
+        # "bthd": the same bytes read as one batch of `count` heads held token-major, (1, s, count, d), through
+        # the layout entry points (the values are random, so any reading of them is as good a workload)
+        self.layout = "bhtd"
 
     def _check(self, code: int, doing: str) -> None:
         if code != 0:
@@ -261,11 +264,22 @@ class Shard:
 
     def forward(self) -> None:
         q, k, v = (t.data_ptr() for t in self.dev[:3])
+        if self.layout == "bthd":
+            self._check(self.lib.limn_b200_sdpa_fwd_layout(q, k, v, None, self.out.data_ptr(), self.lse.data_ptr(), 1, 2, 1, self.count,
+                                                           self.s, self.s, self.d, self.d, int(self.causal), self.scale, None), "sdpa")
+            return
         self._check(self.lib.limn_b200_sdpa_fwd(q, k, v, None, self.out.data_ptr(), self.lse.data_ptr(), 2, self.count, self.s,
                                                 self.s, self.d, self.d, int(self.causal), self.scale, None), "sdpa")
 
     def backward_pass(self) -> None:
         q, k, v, do = (t.data_ptr() for t in self.dev[:4])
+        if self.layout == "bthd":
+            tail = (1, 2, 1, self.count, self.s, self.s, self.d, self.d, int(self.causal), self.scale, None)
+            self._check(self.lib.limn_b200_sdpa_delta_layout(self.out.data_ptr(), do, self.delta.data_ptr(), 1, 2, 1, self.count, self.s, self.d, None), "row dot")
+            self._check(self.lib.limn_b200_sdpa_bwd_q_layout(q, k, v, do, self.lse.data_ptr(), self.delta.data_ptr(), None, self.dq.data_ptr(), *tail), "sdpa_bwd_q")
+            self._check(self.lib.limn_b200_sdpa_bwd_kv_layout(q, k, v, do, self.lse.data_ptr(), self.delta.data_ptr(), None, self.dk.data_ptr(),
+                                                              self.dv.data_ptr(), *tail), "sdpa_bwd_kv")
+            return
         tail = (2, self.count, self.s, self.s, self.d, self.d, int(self.causal), self.scale, None)
         self._check(self.lib.limn_b200_sdpa_delta(self.out.data_ptr(), do, self.delta.data_ptr(), 2, self.count * self.s, self.d, None), "row dot")
         self._check(self.lib.limn_b200_sdpa_bwd_q(q, k, v, do, self.lse.data_ptr(), self.delta.data_ptr(), None, self.dq.data_ptr(), *tail), "sdpa_bwd_q")
@@ -337,6 +351,23 @@ def other_workloads(args, main: str, world: int, rank: int, torch, device, barri
             entry["fwd_bwd_tflops"] = 3.5 * fwd_flops(b * h, s, d, causal) / (step_ms * 1e-3) / 1e12
             entry["fwd_bwd_pct_of_measured_peak"] = 100 * entry["fwd_bwd_tflops"] / world / tensor_peak
             entry["includes"] = "sdpa + row dot (delta) + sdpa_bwd_q + sdpa_bwd_kv; credited 3.5x forward flops, executed 4.5x"
+        # the same step with the operands held token-major, (batch, t, heads, hd), through the layout entry points,
+        # and what the permute copies that layout makes unnecessary cost (torch, one per operand and result)
+        shard.layout = "bthd"
+        for _ in range(3):
+            shard.step()
+        barrier()
+        entry["token_major_ms"] = max_over_ranks(timed(shard, steps, shard.step)) / steps
+        shard.layout = "bhtd"
+        tensors = shard.dev[:4 if backward else 3] + [shard.out] + ([shard.dq, shard.dk, shard.dv] if backward else [])
+
+        def permute_copies():
+            for t in tensors:
+                t.view(1, s, count, d).transpose(1, 2).contiguous()
+
+        permute_copies()
+        barrier()
+        entry["permute_copies_ms"] = max_over_ranks(timed(shard, steps, permute_copies)) / steps
         found[name] = entry
         del shard
         torch.cuda.empty_cache()
