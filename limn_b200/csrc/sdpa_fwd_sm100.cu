@@ -272,14 +272,6 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         for (int kk = 4 * part; kk < 4 * part + 4; ++kk)
           mma_ts_lo(c, a + kk * 8, v_lo + kk * (16 * 128 / 16), idesc_pv, (kk > 0 || !first) ? 1u : 0u);
       };
-      auto issue_pv_piece = [&](int t, int stage, int piece, bool first) {
-        const uint32_t v_lo = desc_lo(base + L::kVOff + stage * L::kTileBytes, L::kAtomBytes);
-        const uint32_t c = tmem + L::kOCol + t * D;
-        const uint32_t a = tmem + L::kSCol + t * 128;
-#pragma unroll
-        for (int kk = 2 * piece; kk < 2 * piece + 2; ++kk)
-          mma_ts_lo(c, a + kk * 8, v_lo + kk * (16 * 128 / 16), idesc_pv, (kk > 0 || !first) ? 1u : 0u);
-      };
       unsigned q_uses[kQTiles] = {0u, 0u};  // items finished in which Q tile t had rows
       unsigned tiles[kQTiles] = {0u, 0u};   // key tiles Q tile t has been through, over all items
       unsigned step = 0;                    // key tiles consumed so far, over all items
@@ -321,19 +313,6 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           for (int t = 0; t < kQTiles; ++t) {
             if (!ok || j >= item.n_kv[t]) continue;
             TRACE_EVENT(100 + t);
-#ifdef LIMN_FWD_QUARTERS
-            // the item's first product overwrites O_t: the previous item's epilogue must have read it
-            if (j == 0) ok = mbar_wait(bar(B::o_free + t), (q_uses[t] & 1u) ^ 1u, prm.status, 0x0270u | t);
-#pragma unroll
-            for (int piece = 0; piece < 4 && ok; ++piece) {
-              ok = mbar_wait(bar(B::p_full + t), piece & 1, prm.status, 0x0230u | t);  // four completions per tile
-              if (!ok) break;
-              tc_fence_after_sync();
-              issue_pv_piece(t, stage, piece, j == 0);
-            }
-            if (!ok) break;
-            TRACE_EVENT(110 + t);
-#else
             const uint32_t phase = tiles[t] & 1u;
             // the product starts on the first 64 keys while the softmax is still on the last 64
             ok = mbar_wait(bar(B::p_half + t), phase, prm.status, 0x0260u | t);
@@ -348,7 +327,6 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             TRACE_EVENT(110 + t);
             tc_fence_after_sync();
             issue_pv(t, stage, 1, j == 0);
-#endif
             TRACE_EVENT(120 + t);
             ++tiles[t];
             if (j + 1 < item.n_kv[t]) {
@@ -476,51 +454,6 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const float shift = (kMask && m == -INFINITY) ? 0.f : -m * sl2;
       const uint64_t shift2 = f2_pack(shift, shift);
       uint64_t sum2[2] = {0ull, 0ull};
-#ifdef LIMN_FWD_QUARTERS
-      // P_t goes over in four pieces of 32 keys, each handed to the MMA warp (p_full completes four times per
-      // tile) once the next piece's exponentials have covered its store's latency; only the last piece's two
-      // MMAs are then left between the end of the softmax and the next tile's scores.
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        if (c == 1) {
-          // O_t was last written by the PV of tile j-1, which s_full also covers. It is rescaled before any of
-          // this tile's P_t is handed over.
-          if (j > 0 && __any_sync(0xffffffffu, moves)) {
-#pragma unroll
-            for (int oc = 0; oc < D / 32; ++oc) {
-              uint32_t o[32];
-              tmem_ld32(t_o + 32 * oc, o);
-              tmem_ld_wait();
-#pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-              tmem_st32(t_o + 32 * oc, o);
-            }
-          }
-        }
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const uint64_t x2 = f2_fma(f2_pack_bits(s[c][i], s[c][i + 1]), sl2_2, shift2);
-          float p0, p1;
-          if (!kMask && ((i >> 1) & 7) < kPolyPairsOf8) {
-            exp2_poly2(x2, p0, p1);
-          } else {
-            f2_unpack(x2, p0, p1);
-            p0 = exp2_approx(p0);
-            p1 = exp2_approx(p1);
-          }
-          sum2[(i >> 1) & 1] = f2_add(sum2[(i >> 1) & 1], f2_pack(p0, p1));
-          packed[i >> 1] = kFp16 ? pack_f16(p0, p1) : pack_bf16(p0, p1);
-        }
-        if (c > 0) {
-          // the previous piece's store was issued a piece of exponentials ago; hand it over
-          tmem_st_wait();
-          tc_fence_before_sync();
-          mbar_arrive(bar(B::p_full + t));
-        }
-        tmem_st16(t_s + 16 * c, packed);
-      }
-#else
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         if (h == 1) {
@@ -568,7 +501,6 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
         tmem_st32(t_s + 32 * h, packed);
       }
-#endif
       TRACE_EVENT(5);
       float sum_a, sum_b, sum_c, sum_d;
       f2_unpack(sum2[0], sum_a, sum_b);
