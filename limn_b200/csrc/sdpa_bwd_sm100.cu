@@ -51,8 +51,8 @@ constexpr int kMmaWarp = 9;
 constexpr uint32_t kTmemCols = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 // Early schedule: of every 8 pairs of scores, how many take exp2 as a cubic on the FMA pipe instead of on the
-// special-function unit. Measured on B200: 2 of 8 gains 3 % in the dQ pass at head dim 64 and loses 13 % in the
-// dK/dV pass, so the default is none.
+// special-function unit. Measured on B200 with the work-fetching kernels: 1 or 2 of 8 lose 3 to 5 % in the dQ
+// pass and 7 % or more in the dK/dV pass at head dim 64, so the default is none.
 #ifndef LIMN_BWD_POLY_PAIRS
 #define LIMN_BWD_POLY_PAIRS 0
 #endif
