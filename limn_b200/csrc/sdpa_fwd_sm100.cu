@@ -44,10 +44,18 @@ constexpr int kMmaWarp = 9;
 constexpr uint32_t kTmemCols = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleSlack = 8.f;   // log2 units a row maximum may outgrow its reference before O is rescaled
-#ifndef LIMN_POLY_PAIRS
-#define LIMN_POLY_PAIRS 2
+// Of every 8 pairs of scores, how many take exp2 as a cubic on the FMA pipe instead of on the special-function
+// unit. Measured on B200: one pair is best at head dim 64 and without a causal mask (1 to 2.5 % over none or two),
+// none under a causal mask at head dim 128 (1 to 2 % over one or two); three or more are slower everywhere.
+// LIMN_POLY_PAIRS overrides the choice for experiments.
+template <int D, bool kCausal>
+constexpr int poly_pairs_of_8() {
+#ifdef LIMN_POLY_PAIRS
+  return LIMN_POLY_PAIRS;
+#else
+  return (D == 128 && kCausal) ? 0 : 1;
 #endif
-constexpr int kPolyPairsOf8 = LIMN_POLY_PAIRS;       // of every 8 pairs of scores, how many take exp2 on the FMA pipe instead of the SFU
+}
 
 template <int D>
 struct FwdLayout {
@@ -482,7 +490,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             float p0, p1;
             // (not under a key mask: the cubic turns a hidden key's -inf into 2^-125 rather than 0, which a row
             // with no visible key at all would then mistake for a denominator)
-            if (!kMask && ((i >> 1) & 7) < kPolyPairsOf8) {
+            if (!kMask && ((i >> 1) & 7) < poly_pairs_of_8<D, kCausal>()) {
               exp2_poly2(x2, p0, p1);
             } else {
               f2_unpack(x2, p0, p1);
