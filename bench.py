@@ -101,7 +101,7 @@ def forward_traffic(workload: str, problems: int):
     """DRAM bytes (read + write) of one forward launch, from the ncu captures summarised under profiles/:
     measured on a subset of the workload's problems and scaled by the problem count, to which it is
     proportional (every problem's tensors cross HBM once). None where no capture exists."""
-    per_problem = {"prefill_4k": (201.626112e6 + 46.807296e6) / 64, "encoder_2k": (100.735488e6 + 16.224768e6) / 128}
+    per_problem = {"prefill_4k": (202.346496e6 + 47.651328e6) / 64, "encoder_2k": (102.376448e6 + 18.868224e6) / 128}
     return per_problem[workload] * problems if workload in per_problem else None
 
 
