@@ -77,8 +77,11 @@ int limn_b200_sdpa_bwd_kv(const void* q, const void* k, const void* v, const voi
  *   `status_out` is an optional device word that receives the kernels' status (0 = no wait gave up).
  *   Limits: bh * t_q <= LIMN_B200_STATIC_MAX_ROWS, else LIMN_B200_UNSUPPORTED and nothing is launched.
  *   All calls on a device share the array: calls that can overlap on the GPU race and must be
- *   serialised by the caller. The first call on a device looks the array's address up and should
- *   come before any stream capture on that device. */
+ *   serialised by the caller. The first call on a device looks the array's address up (and, with CUDA's lazy
+ *   module loading, is when the driver places the array and the kernels on that GPU): make it before any
+ *   stream capture on that device and while the device still has ~10 MiB free, or set CUDA_MODULE_LOADING=EAGER.
+ *   Every argument check happens before anything is enqueued: a refused call launches nothing and leaves the
+ *   array untouched. */
 #define LIMN_B200_STATIC_MAX_ROWS (1LL << 20)
 int limn_b200_sdpa_bwd_q_static(const void* q, const void* k, const void* v, const void* out,
                                 const void* dout, const void* lse, const void* key_mask,
@@ -141,9 +144,21 @@ const char* limn_b200_last_error(void);
 int limn_b200_version(void);
 
 /* Kernels that wait (on TMA or tensor-core completion) give up after a bounded time and
- * record a code in a per-device status word instead of hanging. This reads the word of the
- * current device after synchronising it, and clears it; 0 means no kernel gave up. */
+ * record a code in a per-device status word instead of hanging; kernels launched on that device
+ * afterwards return at once, writing nothing, until the word has been read. This synchronises the
+ * current device, reads its word into *status and clears it. Returns LIMN_B200_OK with *status == 0
+ * when no kernel gave up, LIMN_B200_DEVICE_TIMEOUT with *status = 0x5741rrbb (role rr, barrier bb)
+ * when one did. The reference reports a failed kernel from its batch barrier
+ * (limn/backend_cuda.py:349 through check(), :154-162); limn_b200.install() makes finish() call this. */
 int limn_b200_device_status(unsigned int* status);
+
+/* Diagnostic, no counterpart in the reference: one warp waits on a barrier nobody arrives at, with the
+ * production kernels' bounded wait but a budget of `budget_ticks` clock ticks (at most 1e8), so that the wait
+ * runs out, the status word of the current device receives 0x57417e57 and the kernel returns normally.
+ * `gave_up` is an optional device word that receives 1 (the wait ran out) or 0. It lets a test walk the
+ * give-up path (status code, later launches standing down, counters left clean, read-and-clear) without
+ * making any production kernel misbehave and without hanging or faulting anything. */
+int limn_b200_wait_probe(long long budget_ticks, unsigned int* gave_up, void* stream);
 
 /* ---- plumbing for hosts without a CUDA binding of their own (tests, benchmark) ----
  * limn itself allocates and copies through the driver API (limn/backend_cuda.py:297-326)

@@ -7,16 +7,15 @@ use raises. Build it with `python -m limn_b200.build`.
 from __future__ import annotations
 
 import ctypes
-import os
 from ctypes import POINTER, c_char_p, c_double, c_float, c_int, c_longlong, c_uint, c_ulonglong, c_void_p
 from pathlib import Path
 
-# LIMN_B200_LIBRARY names another build of the same library (a debugging aid: comparing kernel variants)
-LIB_PATH = Path(os.environ.get("LIMN_B200_LIBRARY") or Path(__file__).resolve().parent / "liblimn_b200.so")
+LIB_PATH = Path(__file__).resolve().parent / "liblimn_b200.so"
 
 # dtype codes of enum limn_b200_dtype, by the names limn's DType carries (limn/ops.py:24-27)
 DTYPE_CODES = {"float32": 0, "float16": 1, "bfloat16": 2, "float64": 3}
 PATH_GENERAL, PATH_TCGEN05 = 0, 1
+OK, BAD_ARGUMENT, UNSUPPORTED, CUDA_ERROR, DEVICE_TIMEOUT = 0, 1, 2, 3, 4  # enum limn_b200_status
 
 _P = c_void_p
 _SHAPE = (c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_double, _P)  # dtype, bh, t_q, t_k, hd, hd_v, causal, scale, stream
@@ -39,6 +38,7 @@ SIGNATURES = {
     "limn_b200_last_error": (c_char_p, ()),
     "limn_b200_version": (c_int, ()),
     "limn_b200_device_status": (c_int, (POINTER(c_uint),)),
+    "limn_b200_wait_probe": (c_int, (c_longlong, _P, _P)),
     "limn_b200_device_count": (c_int, (POINTER(c_int),)),
     "limn_b200_set_device": (c_int, (c_int,)),
     "limn_b200_mem_alloc": (c_int, (POINTER(c_void_p), c_ulonglong)),

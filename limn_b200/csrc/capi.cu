@@ -39,6 +39,7 @@ int fail(int code, const char* fmt, ...) {
 
 void clear_error() { g_error[0] = '\0'; }
 void note_launches(int n) { g_launches += n; }
+void reset_launches() { g_launches = 0; }
 
 int cuda_fail(cudaError_t err, const char* doing) {
   return fail(LIMN_B200_CUDA_ERROR, "cuda: %s: %s", doing, cudaGetErrorString(err));
@@ -191,9 +192,7 @@ Problem problem(const void* q, const void* k, const void* v, const void* mask, i
 
 }  // namespace
 
-int dispatch_op(Op op, const char* name, const Problem& p) {
-  clear_error();
-  g_launches = 0;
+int validate_op(Op op, const char* name, const Problem& p) {
   if (int rc = check_problem(name, p)) return rc;
   const bool have_inputs = p.q && p.k && p.v;
   bool have_rest = true;
@@ -203,13 +202,20 @@ int dispatch_op(Op op, const char* name, const Problem& p) {
     case Op::BwdKV: have_rest = p.dout && p.lse_in && p.delta && p.dk && p.dv; break;
   }
   if (!have_inputs || !have_rest) return fail(LIMN_B200_BAD_ARGUMENT, "%s: a required pointer is null", name);
-  if (p.bh == 0) return LIMN_B200_OK;
-  if (tcgen05_serves(op, p)) return tcgen05_launch(op, p);
-  if (p.layout != LIMN_B200_BHTD)
+  if (p.bh > 0 && !tcgen05_serves(op, p) && p.layout != LIMN_B200_BHTD)
     return fail(LIMN_B200_UNSUPPORTED,
                 "%s: the (batch, t, heads, hd) layout is served for f16/bf16 with hd == hd_v in {64, 128}; make the "
                 "operands contiguous as (batch, heads, t, hd) for anything else",
                 name);
+  return LIMN_B200_OK;
+}
+
+int dispatch_op(Op op, const char* name, const Problem& p) {
+  clear_error();
+  g_launches = 0;
+  if (int rc = validate_op(op, name, p)) return rc;
+  if (p.bh == 0) return LIMN_B200_OK;
+  if (tcgen05_serves(op, p)) return tcgen05_launch(op, p);
   return general_launch(op, p);
 }
 
@@ -336,8 +342,12 @@ int limn_b200_device_status(unsigned int* status) {
   if (int rc = status_word(&word)) return rc;
   LIMN_CUDA(cudaDeviceSynchronize(), "waiting for the device before reading its status word");
   LIMN_CUDA(cudaMemcpy(status, word, sizeof(unsigned int), cudaMemcpyDeviceToHost), "reading the device status word");
-  if (*status != 0) LIMN_CUDA(cudaMemset(word, 0, sizeof(unsigned int)), "clearing the device status word");
-  return LIMN_B200_OK;
+  if (*status == 0) return LIMN_B200_OK;
+  LIMN_CUDA(cudaMemset(word, 0, sizeof(unsigned int)), "clearing the device status word");
+  return fail(LIMN_B200_DEVICE_TIMEOUT,
+              "a kernel gave up on a bounded wait (status 0x%08x: role %u, barrier %u); kernels launched after it on this "
+              "device wrote nothing until now",
+              *status, (*status >> 8) & 0xffu, *status & 0xffu);
 }
 
 /* ---- plumbing ---- */

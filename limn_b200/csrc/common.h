@@ -47,6 +47,7 @@ enum class Op { Fwd, BwdQ, BwdKV };
 int fail(int code, const char* fmt, ...);
 void clear_error();
 void note_launches(int n);
+void reset_launches();
 
 // cudaError_t -> status code with a message naming what was being done.
 int cuda_fail(cudaError_t err, const char* doing);
@@ -70,7 +71,9 @@ int work_group(const Problem& p, long long items, int sms);
 // Streaming multiprocessors of the current device.
 int sm_count(int* count);
 
-// Argument checks and dispatch shared by every entry point for the three ops.
+// Argument checks and dispatch shared by every entry point for the three ops. validate_op only checks
+// (extents, dtype, required pointers, layout support) and launches nothing; dispatch_op checks, then launches.
+int validate_op(Op op, const char* name, const Problem& p);
 int dispatch_op(Op op, const char* name, const Problem& p);
 
 // Kernel families. Each returns a status code and enqueues on p.stream.

@@ -820,7 +820,9 @@ int launch_bwd(const Problem& p) {
   prm.q_tiles = (p.t_q + kTile - 1) / kTile;
   prm.kv_tiles = (p.t_k + kTile - 1) / kTile;
 #ifdef LIMN_TRACE
-  prm.trace = reinterpret_cast<long long*>(strtoull(getenv("LIMN_TRACE_PTR"), nullptr, 16));
+  const char* trace_ptr = getenv("LIMN_TRACE_PTR");
+  if (trace_ptr == nullptr) return fail(LIMN_B200_BAD_ARGUMENT, "this is a -DLIMN_TRACE build: set LIMN_TRACE_PTR to the trace buffer's device address");
+  prm.trace = reinterpret_cast<long long*>(strtoull(trace_ptr, nullptr, 16));
 #endif
   prm.scale = static_cast<float>(p.scale);
   const long long items = p.bh * (kKV ? prm.kv_tiles : prm.q_tiles);

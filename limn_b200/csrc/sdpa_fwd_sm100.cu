@@ -599,7 +599,9 @@ int launch_fwd(const Problem& p) {
   prm.q_pairs = (p.t_q + kQTiles * kTileRows - 1) / (kQTiles * kTileRows);
   prm.kv_tiles = (p.t_k + kTileRows - 1) / kTileRows;
 #ifdef LIMN_TRACE
-  prm.trace = reinterpret_cast<long long*>(strtoull(getenv("LIMN_TRACE_PTR"), nullptr, 16));
+  const char* trace_ptr = getenv("LIMN_TRACE_PTR");
+  if (trace_ptr == nullptr) return fail(LIMN_B200_BAD_ARGUMENT, "this is a -DLIMN_TRACE build: set LIMN_TRACE_PTR to the trace buffer's device address");
+  prm.trace = reinterpret_cast<long long*>(strtoull(trace_ptr, nullptr, 16));
 #endif
   prm.scale = static_cast<float>(p.scale);
   const long long items = p.bh * prm.q_pairs;

@@ -71,21 +71,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return done != 0;
 }
 
-// Wait for the phase with the given parity to complete, or give up: returns false after the
-// tick budget, having recorded `tag` in the status word. Callers leave their loops on false.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned* status, unsigned tag) {
+// Wait for the phase with the given parity to complete, or give up: returns false after `budget` clock64()
+// ticks, having recorded `tag` in the status word. Callers leave their loops on false.
+__device__ __forceinline__ bool mbar_wait_for(uint32_t bar, uint32_t parity, unsigned* status, unsigned tag, long long budget) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
   for (;;) {
 #pragma unroll 1
     for (int spin = 0; spin < 256; ++spin)
       if (mbar_try_wait(bar, parity)) return true;
-    if (clock64() - start > kWaitBudgetTicks) {
+    if (clock64() - start > budget) {
       atomicCAS(status, kStatusOk, kStatusWaitTimeout | (tag & 0xffffu));
       return false;
     }
     if (*reinterpret_cast<volatile unsigned*>(status) != kStatusOk) return false;  // someone else already gave up
   }
+}
+// The wait every kernel uses: the budget is kWaitBudgetTicks.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned* status, unsigned tag) {
+  return mbar_wait_for(bar, parity, status, tag, kWaitBudgetTicks);
 }
 
 // ---- fences ----

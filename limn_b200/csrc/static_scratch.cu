@@ -9,8 +9,9 @@
 // back either fails or takes memory the pool believes it owns. Code that runs where CUDA's
 // allocation calls are not permitted at all, because they synchronise the device or may not be
 // issued from that context, cannot call them either. For those hosts this entry point keeps
-// both pieces in one array that is part of the library image: it exists from the moment the
-// library is loaded on a GPU until the process exits, and no call ever allocates or frees.
+// both pieces in one array that is part of the library's device image: no call allocates or
+// frees, the array simply comes with the code. (CUDA places a library's device image, this
+// array included, on a GPU when the library is first used there, see below.)
 //
 // The price is a fixed capacity and shared state:
 //   * the array holds delta for at most LIMN_B200_STATIC_MAX_ROWS = 2^20 query rows
@@ -25,7 +26,13 @@
 //
 // The first call on each device looks the array's device address up. That is a host-side
 // query, done once per device with that device current; it should happen before any stream
-// capture is begun on that device.
+// capture is begun on that device. With CUDA's default lazy module loading it is also the
+// moment the driver places this file's device image (the 8 MiB array) and, at their first
+// launch, the images of the row-dot and dQ kernels on that GPU. A host whose pool is about to
+// take every free byte should therefore make one small call on each device first (or run with
+// CUDA_MODULE_LOADING=EAGER, which places everything when the library is loaded): otherwise that
+// first call can fail with an out-of-memory error from the driver, which is reported as
+// LIMN_B200_CUDA_ERROR.
 #include <cuda_runtime.h>
 
 #include <mutex>
@@ -73,6 +80,9 @@ extern "C" int limn_b200_sdpa_bwd_q_static(const void* q, const void* k, const v
                                            unsigned int* status_out, int dtype, long long bh, int t_q, int t_k,
                                            int hd, int hd_v, int causal, double scale, void* stream) {
   clear_error();
+  reset_launches();
+  // Every check comes before the first thing put on the stream: a refused call enqueues nothing and leaves
+  // the shared array as it was.
   if (!out || !dout) return fail(LIMN_B200_BAD_ARGUMENT, "sdpa_bwd_q_static: a required pointer is null");
   if (bh < 0 || t_q <= 0) return fail(LIMN_B200_BAD_ARGUMENT, "sdpa_bwd_q_static: extents must be positive");
   const long long rows = bh * t_q;
@@ -81,28 +91,25 @@ extern "C" int limn_b200_sdpa_bwd_q_static(const void* q, const void* k, const v
                 "sdpa_bwd_q_static: %lld query rows (bh * t_q) exceed the %lld the static scratch holds; "
                 "use limn_b200_sdpa_bwd_q with a delta buffer of your own",
                 rows, kMaxRows);
-  unsigned char* scratch = nullptr;
-  if (int rc = scratch_address(&scratch)) return rc;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  unsigned int* status = reinterpret_cast<unsigned int*>(scratch);
-  void* delta = scratch + kStatusBytes;
-
-  unsigned int* schedule = reinterpret_cast<unsigned int*>(scratch + 64);
-  LIMN_CUDA(cudaMemsetAsync(scratch, 0, 128, s), "clearing the static status word and work counters");
-  int launches = 0;
-  if (rows > 0) {
-    if (int rc = general_delta(out, dout, delta, dtype, rows, hd_v, s)) return rc;
-    launches = 1;
-  }
   Problem p;
   p.q = q, p.k = k, p.v = v, p.mask = key_mask;
-  p.dout = dout, p.lse_in = lse, p.delta = delta, p.dq = dq;
+  p.dout = dout, p.lse_in = lse, p.dq = dq;
   p.dtype = dtype, p.bh = bh, p.t_q = t_q, p.t_k = t_k, p.hd = hd, p.hd_v = hd_v;
-  p.causal = causal != 0, p.scale = scale, p.stream = s;
+  p.causal = causal != 0, p.scale = scale, p.stream = static_cast<cudaStream_t>(stream);
+  p.delta = out;  // any non-null value for the pointer checks; the real address is filled in below
+  if (int rc = validate_op(Op::BwdQ, "sdpa_bwd_q_static", p)) return rc;
+  unsigned char* scratch = nullptr;
+  if (int rc = scratch_address(&scratch)) return rc;
+  cudaStream_t s = p.stream;
+  unsigned int* status = reinterpret_cast<unsigned int*>(scratch);
+  p.delta = scratch + kStatusBytes;
   p.status = status;
-  p.schedule = schedule;
+  p.schedule = reinterpret_cast<unsigned int*>(scratch + 64);
+  if (rows == 0) return LIMN_B200_OK;
+  LIMN_CUDA(cudaMemsetAsync(scratch, 0, 128, s), "clearing the static status word and work counters");
+  if (int rc = general_delta(out, dout, scratch + kStatusBytes, dtype, rows, hd_v, s)) return rc;
   if (int rc = dispatch_op(Op::BwdQ, "sdpa_bwd_q_static", p)) return rc;
-  note_launches(launches);
+  note_launches(1);  // the row dot, beside what dispatch_op counted
   if (status_out)
     LIMN_CUDA(cudaMemcpyAsync(status_out, status, sizeof(unsigned int), cudaMemcpyDeviceToDevice, s),
               "handing the status word to the caller");

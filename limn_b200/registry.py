@@ -9,7 +9,7 @@ changes, and tensor.py's `has_custom` checks (limn/tensor.py:559, :696) keep pas
 
 A builder reads only what the node states: `node.arg.name`, `node.arg.params == (causal,
 scale)`, `node.arg.outs`, and each `node.srcs[i].shape` / `.dtype.name`; so it works on
-limn's Node or on limn_b200.host's stand-ins alike. A Runner reads `.ptr` off every buffer
+limn's Node or on a test's stand-in alike. A Runner reads `.ptr` off every buffer
 on every call and keeps none of them, because a captured plan is replayed against new
 buffers each time (limn/capture.py:152-168). It launches on the legacy default stream, where
 limn's own kernels run (limn/backend_cuda.py:413), and does not synchronise: the device's
@@ -22,7 +22,9 @@ import math
 from collections.abc import Callable
 from typing import Any
 
-from limn_b200._lib import DTYPE_CODES, check, lib
+import ctypes
+
+from limn_b200._lib import DEVICE_TIMEOUT, DTYPE_CODES, check, lib
 
 SDPA, SDPA_BWD_Q, SDPA_BWD_KV = "sdpa", "sdpa_bwd_q", "sdpa_bwd_kv"  # limn/sdpa.py:43-45
 NAMES = (SDPA, SDPA_BWD_Q, SDPA_BWD_KV)
@@ -90,6 +92,7 @@ def build_sdpa(node: Any) -> Runner:
         ins, (out, lse) = _pointers(form, inputs, outs)
         mask = ins[3] if form.has_mask else None
         check(fn(ins[0], ins[1], ins[2], mask, out, lse, *tail), "launching sdpa")
+        _note_launch()
 
     return run
 
@@ -104,6 +107,7 @@ def build_sdpa_bwd_q(node: Any) -> Runner:
         ins, (dq,) = _pointers(form, inputs, outs)
         mask = ins[6] if form.has_mask else None
         check(fn(ins[0], ins[1], ins[2], ins[3], ins[4], ins[5], mask, dq, *tail), "launching sdpa_bwd_q")
+        _note_launch()
 
     return run
 
@@ -118,6 +122,7 @@ def build_sdpa_bwd_kv(node: Any) -> Runner:
         ins, (dk, dv) = _pointers(form, inputs, outs)
         mask = ins[6] if form.has_mask else None
         check(fn(ins[0], ins[1], ins[2], ins[3], ins[4], ins[5], mask, dk, dv, *tail), "launching sdpa_bwd_kv")
+        _note_launch()
 
     return run
 
@@ -129,13 +134,59 @@ BUILDERS: dict[str, Callable[[Any], Runner]] = {
 }
 
 
+# Whether a Runner has launched since the last status check: finish() only pays for the check then.
+_launched_since_check = False
+
+
+def _note_launch() -> None:
+    global _launched_since_check
+    _launched_since_check = True
+
+
+def check_device_status(doing: str = "waiting for the batch") -> None:
+    """Raise if a kernel of this library gave up on a bounded wait since the last check.
+
+    A kernel that waits (on a TMA copy or on the tensor pipe) does so for a bounded time; when
+    the time runs out it records a code in a per-device status word and returns, and every
+    later kernel on that device returns at once without writing its outputs until the word has
+    been read. The reference turns a failed kernel into a RuntimeError at its batch barrier
+    (limn/backend_cuda.py:349 through check(), :154-162); this is the same for ours."""
+    global _launched_since_check
+    if not _launched_since_check:
+        return
+    _launched_since_check = False
+    word = ctypes.c_uint(0)
+    code = lib().limn_b200_device_status(ctypes.byref(word))
+    if code != DEVICE_TIMEOUT:
+        check(code, "reading the device status word")
+    if word.value:
+        raise RuntimeError(
+            f"cuda: {doing}: a limn_b200 kernel gave up on a bounded wait (status 0x{word.value:08x}); "
+            "outputs of this batch are incomplete"
+        )
+
+
 def install(device: Any) -> Any:
     """Register the three builders on a device that has a `custom` registry (limn's
     CompiledDevice, limn/jit.py:103-135). Loads the shared library first, so a missing or
-    unloadable library fails here rather than at the first step."""
+    unloadable library fails here rather than at the first step.
+
+    The device's finish() (limn's one synchronise per batch, limn/jit.py:183) is wrapped so that
+    after it returns the kernels' status word is read whenever one of our Runners ran in the
+    batch: a kernel that gave up surfaces as a RuntimeError at the same place a failed kernel of
+    the reference's does, instead of as unwritten buffers later."""
     lib()
     if not hasattr(device, "custom"):
         raise TypeError(f"limn_b200.install: {type(device).__name__} has no CUSTOM registry")
     for name, build in BUILDERS.items():
         device.custom[name] = build
+    inner = getattr(device, "finish", None)
+    if callable(inner) and not getattr(inner, "_limn_b200_checked", False):
+
+        def finish() -> None:
+            inner()
+            check_device_status()
+
+        finish._limn_b200_checked = True  # type: ignore[attr-defined]
+        device.finish = finish
     return device

@@ -12,7 +12,7 @@ import ctypes
 
 import numpy as np
 
-from limn_b200._lib import check, lib
+from limn_b200._lib import DEVICE_TIMEOUT, check, lib
 
 
 class DeviceBuffer:
@@ -77,7 +77,9 @@ def synchronize() -> None:
 def device_status() -> int:
     """The current device's kernel status word (0 = no kernel gave up on a wait); clears it."""
     word = ctypes.c_uint()
-    check(lib().limn_b200_device_status(ctypes.byref(word)), "reading the device status word")
+    code = lib().limn_b200_device_status(ctypes.byref(word))
+    if code != DEVICE_TIMEOUT:  # a set word is this function's answer, not its failure
+        check(code, "reading the device status word")
     return word.value
 
 

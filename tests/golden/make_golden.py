@@ -12,6 +12,7 @@ does not have to. bfloat16 arrays are stored as their uint16 bit patterns ("<nam
 
 from __future__ import annotations
 
+import os
 import sys
 from pathlib import Path
 from types import SimpleNamespace
@@ -75,7 +76,9 @@ def store(bundle: dict, key: str, array: np.ndarray) -> None:
 
 
 def main() -> None:
-    checkout = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    # the reference checkout: an argument, LIMN_REFERENCE, or the copy the build stages under baseline/_ref
+    staged = Path(__file__).resolve().parents[2] / "baseline" / "_ref"
+    checkout = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("LIMN_REFERENCE", str(staged))
     sys.path.insert(0, checkout)
     from limn import sdpa as ref  # the reference's numpy kernels
 

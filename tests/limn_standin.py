@@ -1,8 +1,10 @@
-"""A minimal host for the three ops, shaped like the parts of limn the kernels touch.
+"""Test scaffolding: a minimal host for the three ops, shaped like the parts of limn the kernels touch.
 
-limn itself is the intended host: `limn_b200.install(limn.device.active())` and everything
-else is limn's. This module exists so the same registry, node shapes and call sequence can
-be driven where limn is not importable: it mirrors, by name and meaning,
+limn itself is the host: `limn_b200.install(limn.device.active())` and everything else is
+limn's (tests/test_limn_dropin_gpu.py drives exactly that). This module lets the per-kernel
+parity tests hand the registry builders nodes and buffers without going through limn's
+frontend, so that they can poison outputs, pick odd shapes and read intermediate buffers: it
+mirrors, by name and meaning,
   * DType / the four float dtypes and `accumulate_in` (limn/ops.py:18-27, :53-62),
   * `Custom` and `custom()`: one node per output, siblings sharing srcs (limn/ops.py:108-136),
   * a device with the `custom` registry, `has_custom`, `custom_runner` (limn/jit.py:109-135)

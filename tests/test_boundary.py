@@ -4,6 +4,7 @@ the way limn's own cuda device does."""
 
 from __future__ import annotations
 
+import os
 import re
 import sys
 from pathlib import Path
@@ -12,7 +13,9 @@ import numpy as np
 import pytest
 
 ROOT = Path(__file__).resolve().parent.parent
-REFERENCE = Path("/root/reference")
+# limn itself, where it is at hand: the copy __graft_entry__.build() stages, or a checkout named by LIMN_REFERENCE
+REFERENCE = next((p for p in (Path(os.environ.get("LIMN_REFERENCE", "")), ROOT / "baseline" / "_ref") if (p / "limn" / "sdpa.py").is_file()),
+                 ROOT / "baseline" / "_ref")
 
 
 def declared_functions() -> list[str]:
@@ -84,7 +87,8 @@ def _nodes(host, dtype, qs, ks, vs, causal, mask=False):
 
 
 def test_builders_read_a_node_like_the_reference_does():
-    from limn_b200 import host, registry
+    import limn_standin as host
+    from limn_b200 import registry
 
     out, lse = _nodes(host, host.bfloat16, (2, 3, 100, 64), (2, 3, 100, 64), (2, 3, 100, 64), True)
     assert out.arg.index == 0 and lse.arg.index == 1 and out.srcs is lse.srcs
@@ -102,7 +106,8 @@ def test_builders_read_a_node_like_the_reference_does():
 
 
 def test_builders_refuse_what_the_ops_cannot_be():
-    from limn_b200 import host, registry
+    import limn_standin as host
+    from limn_b200 import registry
 
     with pytest.raises(ValueError, match="square keys"):
         registry.build_sdpa(_nodes(host, host.float32, (4, 8), (5, 8), (5, 8), True)[0])
@@ -130,8 +135,51 @@ def test_install_needs_a_registry():
     assert set(dev.custom) == {"sdpa", "sdpa_bwd_q", "sdpa_bwd_kv"}
 
 
+def test_installed_finish_reports_a_kernel_that_gave_up(monkeypatch):
+    """install() wraps finish(): with a status word set (a fake library here, no GPU), the batch barrier raises
+    the RuntimeError limn raises for a failed kernel (limn/backend_cuda.py:154-162, :349); a batch without one of
+    our launches does not even read the word."""
+    import limn_b200
+    from limn_b200 import registry
+
+    reads = []
+
+    class FakeLibrary:
+        word = 0x57410203
+
+        def limn_b200_device_status(self, ref):
+            reads.append(self.word)
+            ref._obj.value, code = self.word, (4 if self.word else 0)
+            self.word = 0
+            return code
+
+        def limn_b200_last_error(self):
+            return b"a kernel gave up"
+
+    class Device:
+        def __init__(self):
+            self.custom, self.barriers = {}, 0
+
+        def finish(self):
+            self.barriers += 1
+
+    dev = limn_b200.install(Device())
+    limn_b200.install(dev)  # installing twice wraps once
+    fake = FakeLibrary()
+    monkeypatch.setattr(registry, "lib", lambda: fake)
+    monkeypatch.setattr(registry, "_launched_since_check", False)
+    dev.finish()
+    assert reads == [] and dev.barriers == 1
+    registry._note_launch()
+    with pytest.raises(RuntimeError, match=r"cuda: waiting for the batch: .*status 0x57410203"):
+        dev.finish()
+    registry._note_launch()
+    dev.finish()  # the word was cleared by the read
+    assert reads == [0x57410203, 0] and dev.barriers == 3
+
+
 def test_host_validation_matches_the_frontend_messages():
-    from limn_b200 import host
+    import limn_standin as host
 
     z = lambda *s: np.zeros(s, np.float32)
     with pytest.raises(ValueError, match="2D\\+ tensors"):

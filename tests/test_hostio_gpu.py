@@ -14,7 +14,8 @@ BF16 = np.dtype(ml_dtypes.bfloat16)
 
 @pytest.mark.parametrize("backward", [False, True], ids=["forward", "forward+backward"])
 def test_pipeline_matches_device_resident_calls(backward):
-    from limn_b200 import host, runtime
+    import limn_standin as host
+    from limn_b200 import runtime
     from limn_b200.hostio import HostPipeline
 
     bh, t, d = 11, 300, 64
