@@ -24,15 +24,18 @@ class HostPipeline:
 
     Arguments are numpy arrays over pinned memory (`runtime.PinnedArray(...).array`), shaped
     (bh, t, d) for Q, K, V, dO, O, dQ, dK, dV and (bh, t) float32 for L. `chunk` problems are
-    in flight per stage.
+    in flight per stage; by default the batch is cut into at least eight chunks (of at most 16
+    problems), so that upload, kernels and download overlap even when the batch is small.
     """
 
-    def __init__(self, bh: int, t: int, d: int, *, dtype: str = "bfloat16", causal: bool, backward: bool, chunk: int = 16):
+    def __init__(self, bh: int, t: int, d: int, *, dtype: str = "bfloat16", causal: bool, backward: bool, chunk: int | None = None):
         if dtype not in ("bfloat16", "float16"):
             raise ValueError("HostPipeline moves 16-bit storage; other dtypes go through the registry builders")
         self.bh, self.t, self.d, self.causal, self.backward = bh, t, d, causal, backward
         self.code = DTYPE_CODES[dtype]
         self.scale = d ** -0.5
+        if chunk is None:
+            chunk = min(16, -(-bh // 8))
         self.chunk = max(1, min(chunk, bh))
         self.row_bytes = t * d * 2
         self.lib = lib()

@@ -76,6 +76,7 @@ def spread(bh: int, group: int) -> list[int]:
     some in between."""
     middle = (bh // 2 // group) * group
     picks = {0, group - 1, group, middle - 1, middle, middle + group // 2, bh - group, bh - 1, bh // 3, (2 * bh) // 3 + 1}
+    picks |= {(i * (bh - 1)) // 7 for i in range(8)}  # one group only (a small workload): evenly spaced instead
     return sorted(p for p in picks if 0 <= p < bh)
 
 
@@ -121,8 +122,8 @@ def test_delta_matches_the_oracle_row_dot_on_the_oracles_own_output():
         out = rng.standard_normal(shape).astype(np.float32).astype(dtype)
         do = rng.standard_normal(shape).astype(np.float32).astype(dtype)
         rows = shape[0] * shape[1]
-        delta = runtime.empty(rows * 4)
-        check(lib().limn_b200_sdpa_delta(runtime.upload(out).ptr, runtime.upload(do).ptr, delta.ptr, code, rows, shape[2], None), "row dot")
+        delta, out_dev, do_dev = runtime.empty(rows * 4), runtime.upload(out), runtime.upload(do)
+        check(lib().limn_b200_sdpa_delta(out_dev.ptr, do_dev.ptr, delta.ptr, code, rows, shape[2], None), "row dot")
         got = runtime.download(delta, np.float32, shape[:2])
         parity(got, oracle.row_delta(do, out)[..., 0], 1e-5, f"delta {np.dtype(dtype).name} {shape}")
 
