@@ -716,6 +716,163 @@ def gpu_arm(args) -> None:
         dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------- limn itself on the GPU
+
+
+def gpt_step(limn, *, dim: int, heads: int, layers: int, ctx: int, vocab: int = 256, attention_dtype=None):
+    """A byte-level GPT training step shaped like limn's examples/train_stories.py (pre-norm blocks of causal
+    attention and a 4x MLP, learned positions, AdamW, the loss realised with the update), at a width of our
+    choosing and with the attention operands optionally cast to a half-width dtype, which is what puts the
+    layer on the tensor-core kernels. Returns (step(tokens, targets) -> loss, parameters)."""
+    from limn.nn import Embedding, LayerNorm, Linear, parameters
+    from limn.optim import AdamW
+
+    Tensor = limn.Tensor
+
+    class Layer:
+        def __init__(self):
+            self.norm_attention, self.norm_mlp = LayerNorm(dim), LayerNorm(dim)
+            self.to_qkv, self.to_out = Linear(dim, 3 * dim), Linear(dim, dim)
+            self.widen, self.narrow = Linear(dim, 4 * dim), Linear(4 * dim, dim)
+
+        def __call__(self, x):
+            b, t, c = x.shape
+            q, k, v = self.to_qkv(self.norm_attention(x)).reshape(b, t, 3, heads, c // heads).permute(2, 0, 3, 1, 4)
+            if attention_dtype is not None:
+                q, k, v = q.cast(attention_dtype), k.cast(attention_dtype), v.cast(attention_dtype)
+            mixed = q.attention(k, v, causal=True)
+            if attention_dtype is not None:
+                mixed = mixed.cast(limn.float32)
+            x = x + self.to_out(mixed.permute(0, 2, 1, 3).reshape(b, t, c))
+            return x + self.narrow(self.widen(self.norm_mlp(x)).relu())
+
+    class Model:
+        def __init__(self):
+            self.tokens, self.positions = Embedding(vocab, dim), Embedding(ctx, dim)
+            self.layers = [Layer() for _ in range(layers)]
+            self.norm, self.head = LayerNorm(dim), Linear(dim, vocab, bias=False)
+
+        def __call__(self, tokens):
+            x = self.tokens(tokens) + self.positions(Tensor.arange(ctx))
+            for layer in self.layers:
+                x = layer(x)
+            return self.head(self.norm(x))
+
+    model = Model()
+    params = parameters(model)
+    opt = AdamW(params, lr=1e-3)
+
+    def step(tokens, targets):
+        opt.zero_grad()
+        logp = model(tokens).log_softmax(-1)
+        hit = Tensor.arange(vocab).reshape(1, 1, vocab).eq(targets.reshape(*targets.shape, 1))
+        loss = -(logp * hit).sum() / float(targets.numel)
+        loss.backward()
+        opt.step(loss)
+        opt.zero_grad()
+        return loss
+
+    return step, params
+
+
+def limn_arm(workload: str) -> None:
+    """limn itself on cuda:0, in a process of its own: first as it ships (its NVRTC-compiled scalar kernels,
+    limn/cuda_emit.py:921-1083 through limn/backend_cuda.py:352-361), then with limn_b200.install(). Everything goes
+    through Tensor.attention, autograd, the scheduler and the plan executor, under limn's capture, and is timed as
+    limn's own benchmark times (examples/bench_attention.py:29-43): wall clock around replays, each of which ends in
+    the device's finish(), best of three trials. Prints one JSON line."""
+    if not limn_on_path():
+        print(json.dumps({"unavailable": "limn is not staged under baseline/_ref"}))
+        return
+    import limn
+    import limn.device
+
+    import limn_b200
+
+    rng = np.random.default_rng(0)
+
+    def replay_ms(step, args, reps: int) -> float:
+        replayed = limn.capture(step)
+
+        def once() -> float:
+            for _ in range(3):
+                replayed(*args)
+            start = time.perf_counter()
+            for _ in range(reps):
+                replayed(*args)
+            return (time.perf_counter() - start) / reps * 1e3
+
+        return min(once() for _ in range(3))
+
+    def attention_case(name: str, problems: int, reps: int) -> dict:
+        b, h, s, d, causal, backward, mul, v_kind, _seed, _ = WORKLOADS[name]
+        problems = min(problems, b * h)
+        shape = (problems, s, d)
+        data = [rng.standard_normal(shape).astype(np.float32) * m for m in (mul, mul, 1.0)]
+
+        def forward(q, k, v):
+            return q.attention(k, v, causal=causal).realize()
+
+        def train(q, k, v):
+            out = q.attention(k, v, causal=causal)
+            grads = limn.grad((out * out).sum(), [q, k, v])
+            limn.realize(*grads)
+            return tuple(grads)
+
+        entry = {"problems": problems, "of": b * h, "shape": [s, d], "causal": causal}
+        args = tuple(limn.Tensor(a, dtype=limn.bfloat16) for a in data)
+        ms = replay_ms(forward, args, reps)
+        entry["fwd_ms"], entry["fwd_tflops"] = ms, fwd_flops(problems, s, d, causal) / (ms * 1e-3) / 1e12
+        if backward or name == "prefill_4k":
+            args = tuple(limn.Tensor(a, dtype=limn.bfloat16, requires_grad=True) for a in data)
+            ms = replay_ms(train, args, reps)
+            entry["fwd_bwd_ms"], entry["fwd_bwd_tflops"] = ms, 3.5 * fwd_flops(problems, s, d, causal) / (ms * 1e-3) / 1e12
+        return entry
+
+    def gpt_case(reps: int) -> dict:
+        ctx, batch = 256, 32
+        limn.set_seed(0)
+        step, params = gpt_step(limn, dim=512, heads=8, layers=6, ctx=ctx, attention_dtype=limn.bfloat16)
+        tokens = rng.integers(0, 256, size=(batch, ctx + 1)).astype(np.int32)
+        args = (limn.Tensor(tokens[:, :-1]), limn.Tensor(tokens[:, 1:]))
+        ms = replay_ms(step, args, reps)
+        return {"ms_per_step": ms, "tokens_per_s": batch * ctx / (ms * 1e-3), "model": "6 layers, d_model 512, 8 heads x 64, context 256, batch 32, "
+                "float32 model with bfloat16 attention operands, synthetic byte tokens, AdamW step included", "parameters": int(sum(p.numel for p in params))}
+
+    found = {"timing": "wall clock around replays of a captured step, each ending in the device's finish(); best of 3 trials",
+             "kernels_as_shipped": {}, "limn_b200_installed": {}}
+    for label, install in (("kernels_as_shipped", False), ("limn_b200_installed", True)):
+        limn.device.set_device("cuda")
+        if install:
+            limn_b200.install(limn.device.active())
+        try:
+            # the main workload on a subset of its problems (limn's scalar kernels need seconds for all of them), the GPT
+            # attention layer in full, and the whole 6-layer training step around it
+            found[label][workload] = attention_case(workload, 16, 3)
+            if workload != "gpt_layer":
+                found[label]["gpt_layer"] = attention_case("gpt_layer", 256, 10)
+            found[label]["gpt_train_step"] = gpt_case(5)
+        except Exception as err:
+            found[label]["error"] = f"{type(err).__name__}: {err}"[:300]
+        finally:
+            limn.device.set_device("numpy")
+    print(json.dumps(found), flush=True)
+
+
+def limn_subprocess(workload: str) -> dict:
+    """Run limn_arm in a process of its own (limn binds the driver API itself) and return what it printed."""
+    if not (STAGED_LIMN / "limn" / "sdpa.py").is_file():
+        return {"unavailable": "limn is not staged under baseline/_ref"}
+    try:
+        done = subprocess.run([sys.executable, str(Path(__file__).resolve()), "--limn-arm", workload], capture_output=True, text=True, timeout=900)
+        lines = [line for line in done.stdout.splitlines() if line.startswith("{")]
+        if done.returncode != 0 or not lines:
+            return {"unavailable": f"limn arm exited {done.returncode}: {done.stderr[-300:]}"}
+        return json.loads(lines[-1])
+    except Exception as err:
+        return {"unavailable": f"{type(err).__name__}: {err}"[:300]}
+
+
 def profile_case(args) -> None:
     """For profiler captures: the first N problems of a workload, each kernel of the path launched
     `--steps` times after one warm-up pass, nothing timed and nothing printed but a status line.

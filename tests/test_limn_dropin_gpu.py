@@ -234,6 +234,50 @@ def test_capture_replays_against_new_buffers(limn, cudev):
         limn.device.set_device("numpy")
 
 
+def test_a_gpt_training_step_under_capture(limn):
+    """The caller of the GPT attention layer: a two-layer byte-level GPT step shaped like limn's
+    examples/train_stories.py (its model and step, :26-56 and :140-147 there) with bfloat16 attention operands,
+    captured and replayed on limn's cuda device with our kernels installed, against the same step on limn's numpy
+    device from the same seed. Synthetic tokens stand in for the TinyStories text the example downloads."""
+    import bench
+
+    import limn_b200
+
+    tokens = np.random.default_rng(5).integers(0, 256, size=(2, 129)).astype(np.int32)
+    ran = {"sdpa": 0, "sdpa_bwd_q": 0, "sdpa_bwd_kv": 0}
+
+    def losses(device_name: str, install: bool) -> list[float]:
+        limn.device.set_device(device_name)
+        try:
+            if install:
+                dev = limn_b200.install(limn.device.active())
+                for name in ran:
+                    build = dev.custom[name]
+
+                    def counted(node, build=build, name=name):
+                        run = build(node)
+
+                        def counted_run(inputs, outs):
+                            ran[name] += 1
+                            run(inputs, outs)
+
+                        return counted_run
+
+                    dev.custom[name] = counted
+            limn.set_seed(0)
+            step, _ = bench.gpt_step(limn, dim=128, heads=2, layers=2, ctx=128, attention_dtype=limn.bfloat16)
+            replayed = limn.capture(step)
+            return [replayed(limn.Tensor(tokens[:, :-1]), limn.Tensor(tokens[:, 1:])).item() for _ in range(4)]
+        finally:
+            limn.device.set_device("numpy")
+
+    want = losses("numpy", False)
+    got = losses("cuda", True)
+    assert all(count >= 2 * 4 for count in ran.values()), ran  # two layers, four steps (two observed, two replayed)
+    np.testing.assert_allclose(got, want, rtol=5e-3)
+    assert got[-1] < got[0]
+
+
 def test_limns_own_test_files_pass_with_the_builders_installed(tmp_path):
     """limn's tests/test_attention.py and tests/test_jit.py, byte for byte as the reference has them, in a
     process of their own with tests/limn_dropin_plugin.py installing the builders on every CudaDevice."""
