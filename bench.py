@@ -453,6 +453,8 @@ def other_workloads(args, main: str, world: int, rank: int, torch, device, barri
             trials = []
             for _ in range(3):
                 barrier()
+                time.sleep(args.rest_seconds)
+                barrier()
                 trials.append(max_over_ranks(timed(shard, steps, body)) / steps)
             return min(trials)
 
@@ -550,11 +552,19 @@ def gpu_arm(args) -> None:
     # ---- device-resident throughput: K steps, the best of three trials, each the max over ranks ----
     for _ in range(max(args.warmup, 3)):
         shard.step()
+    # Each burst trial starts from the same state: a pause first, so that the board's power averaging has let go
+    # of the trial before (at 1 kW the power cap pulls the SM clock from 1.97 to about 1.6 GHz within some tens
+    # of milliseconds of back-to-back launches; what happens then is the "sustained" entry's business).
+    def rested() -> None:
+        barrier()
+        time.sleep(args.rest_seconds)
+        barrier()
+
     trials = []
     if sampler:
         sampler.begin("timed")
     for _ in range(3):
-        barrier()
+        rested()
         shard.launches = 0
         trial_ms = timed(shard, args.steps, shard.step)
         barrier()
@@ -568,7 +578,7 @@ def gpu_arm(args) -> None:
     # dominant kernel alone (the forward), for the roofline entry
     fwd_trials = []
     for _ in range(3):
-        barrier()
+        rested()
         fwd_trials.append(max_over_ranks(timed(shard, args.steps, shard.forward)) / args.steps)
     fwd_ms = min(fwd_trials)
     fwd_rate = fwd_flops(per_rank, s, d, causal) / (fwd_ms * 1e-3) / 1e12
@@ -692,7 +702,7 @@ def gpu_arm(args) -> None:
             "config": {"workload": workload, "describes": WORKLOADS[workload][-1], "pass": "fwd+bwd" if backward else "fwd",
                        "problems_per_rank": per_rank, "sharding": "(batch, head) problems split evenly over ranks, no data-path collective",
                        "l2": "inputs larger than L2" if per_rank * s * d * 2 * 3 > 126e6 else "inputs smaller than L2 (resident between steps)",
-                       "trials": "best of 3 trials of K steps, each trial the max over ranks"},
+                       "trials": f"best of 3 trials of K steps, each trial the max over ranks and preceded by a {args.rest_seconds} s pause"},
             "trials_ms_per_step": [t / args.steps for t in trials],
             "pct_of_peak": {"of_measured_burst": 100 * value / world / tensor_peak, "of_nominal_2250": 100 * value / world / 2250.0},
             "sustained": sustained,
@@ -904,6 +914,7 @@ def main() -> None:
     parser.add_argument("--profile", type=int, default=0, metavar="N", help="launch the kernels over the first N problems and exit (for ncu)")
     parser.add_argument("--backward", action="store_true", help="with --profile: run the backward kernels even for a forward-only workload")
     parser.add_argument("--no-others", dest="others", action="store_false", help="time only the named workload")
+    parser.add_argument("--rest-seconds", type=float, default=0.5, help="pause before each burst trial")
     parser.add_argument("--sustain-seconds", type=float, default=2.0, help="length of the long timed region (0 to skip it)")
     parser.add_argument("--no-limn", dest="limn", action="store_false", help="skip the runs of limn itself on the GPU")
     parser.add_argument("--limn-arm", default=None, metavar="WORKLOAD", help="run limn itself on cuda:0 (stock kernels, then ours) and print one JSON line")
