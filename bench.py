@@ -344,6 +344,8 @@ class Shard:
         # "bthd": the same bytes read as one batch of `count` heads held token-major, (1, s, count, d), through
         # the layout entry points (the values are random, so any reading of them is as good a workload)
         self.layout = "bhtd"
+        # True: the row dot as a kernel of its own before the dQ pass (what limn's frontend schedules today); False: inside it
+        self.separate_delta = False
 
     def _check(self, code: int, doing: str) -> None:
         if code != 0:
@@ -370,14 +372,18 @@ class Shard:
         q, k, v, do = (t.data_ptr() for t in self.dev[:4])
         if self.layout == "bthd":
             tail = (1, 2, 1, self.count, self.s, self.s, self.d, self.d, int(self.causal), self.scale, None)
-            self._check(self.lib.limn_b200_sdpa_delta_layout(self.out.data_ptr(), do, self.delta.data_ptr(), 1, 2, 1, self.count, self.s, self.d, None), "row dot")
-            self._check(self.lib.limn_b200_sdpa_bwd_q_layout(q, k, v, do, self.lse.data_ptr(), self.delta.data_ptr(), None, self.dq.data_ptr(), *tail), "sdpa_bwd_q")
+            self._check(self.lib.limn_b200_sdpa_bwd_q_fused_layout(q, k, v, self.out.data_ptr(), do, self.lse.data_ptr(), None, self.dq.data_ptr(),
+                                                                   self.delta.data_ptr(), *tail), "sdpa_bwd_q")
             self._check(self.lib.limn_b200_sdpa_bwd_kv_layout(q, k, v, do, self.lse.data_ptr(), self.delta.data_ptr(), None, self.dk.data_ptr(),
                                                               self.dv.data_ptr(), *tail), "sdpa_bwd_kv")
             return
         tail = (2, self.count, self.s, self.s, self.d, self.d, int(self.causal), self.scale, None)
-        self._check(self.lib.limn_b200_sdpa_delta(self.out.data_ptr(), do, self.delta.data_ptr(), 2, self.count * self.s, self.d, None), "row dot")
-        self._check(self.lib.limn_b200_sdpa_bwd_q(q, k, v, do, self.lse.data_ptr(), self.delta.data_ptr(), None, self.dq.data_ptr(), *tail), "sdpa_bwd_q")
+        if self.separate_delta:
+            self._check(self.lib.limn_b200_sdpa_delta(self.out.data_ptr(), do, self.delta.data_ptr(), 2, self.count * self.s, self.d, None), "row dot")
+            self._check(self.lib.limn_b200_sdpa_bwd_q(q, k, v, do, self.lse.data_ptr(), self.delta.data_ptr(), None, self.dq.data_ptr(), *tail), "sdpa_bwd_q")
+        else:
+            self._check(self.lib.limn_b200_sdpa_bwd_q_fused(q, k, v, self.out.data_ptr(), do, self.lse.data_ptr(), None, self.dq.data_ptr(),
+                                                            self.delta.data_ptr(), *tail), "sdpa_bwd_q")
         self._check(self.lib.limn_b200_sdpa_bwd_kv(q, k, v, do, self.lse.data_ptr(), self.delta.data_ptr(), None, self.dk.data_ptr(),
                                                    self.dv.data_ptr(), *tail), "sdpa_bwd_kv")
 
@@ -423,7 +429,7 @@ def timed(shard: Shard, steps: int, body) -> float:
 # Algorithmic HBM bytes of each kernel of the path per (batch, head) problem of S tokens and head dim D in 16-bit
 # storage (every operand and result crosses HBM once; L and delta are float32 per row):
 #   sdpa        reads Q, K, V, writes O, L                    8 S D + 4 S
-#   delta       reads O, dO, writes delta                     4 S D + 4 S
+#   delta       reads O, dO, writes delta                     4 S D + 4 S   (inside sdpa_bwd_q when fused; the bytes are the same)
 #   sdpa_bwd_q  reads Q, K, V, dO, L, delta, writes dQ       10 S D + 8 S
 #   sdpa_bwd_kv reads Q, K, V, dO, L, delta, writes dK, dV   12 S D + 8 S
 def hbm_bytes(kernel: str, bh: int, s: int, d: int) -> float:
@@ -466,7 +472,10 @@ def other_workloads(args, main: str, world: int, rank: int, torch, device, barri
             entry["fwd_bwd_ms"] = step_ms
             entry["fwd_bwd_tflops"] = 3.5 * fwd_flops(b * h, s, d, causal) / (step_ms * 1e-3) / 1e12
             entry["fwd_bwd_pct_of_measured_peak"] = 100 * entry["fwd_bwd_tflops"] / world / tensor_peak
-            entry["includes"] = "sdpa + row dot (delta) + sdpa_bwd_q + sdpa_bwd_kv; credited 3.5x forward flops, executed 4.5x"
+            entry["includes"] = "sdpa + sdpa_bwd_q with the row dot (delta) computed inside it + sdpa_bwd_kv; credited 3.5x forward flops, executed 4.5x"
+            shard.separate_delta = True
+            entry["fwd_bwd_ms_with_a_separate_row_dot_kernel"] = best(shard.step)
+            shard.separate_delta = False
         if s * 2 < 1024:
             # a short-sequence workload is bound by HBM and launch latency, not by the tensor pipe: the same
             # times against the bytes each kernel has to move (hbm_bytes above) and the measured copy bandwidth

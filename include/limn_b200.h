@@ -60,6 +60,18 @@ int limn_b200_sdpa_bwd_q(const void* q, const void* k, const void* v, const void
                          int dtype, long long bh, int t_q, int t_k, int hd, int hd_v,
                          int causal, double scale, void* stream);
 
+/* "sdpa_bwd_q" with the row dot folded in: the same dQ as limn_b200_sdpa_delta followed by limn_b200_sdpa_bwd_q,
+ * one launch and one pass over O and dO fewer. Replaces the pair limn's frontend schedules between the forward and
+ * the backward ops (the reduce of limn/tensor.py:705-706 and emit_sdpa_bwd_q, limn/cuda_emit.py:968-1005).
+ *   out is the forward's O (bh, t_q, hd_v), an input here; delta (bh, t_q) in the statistics dtype is an OUTPUT:
+ *   every CTA computes the statistic of the query rows it owns from their rows of O and dO and leaves it there for
+ *   limn_b200_sdpa_bwd_kv, which needs it for every query it streams and therefore has to run after this call. */
+int limn_b200_sdpa_bwd_q_fused(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                               const void* lse, const void* key_mask,
+                               void* dq, void* delta,
+                               int dtype, long long bh, int t_q, int t_k, int hd, int hd_v,
+                               int causal, double scale, void* stream);
+
 /* "sdpa_bwd_kv": replaces emit_sdpa_bwd_kv (limn/cuda_emit.py:1008-1083); oracle limn/sdpa.py:173-203.
  *   dk (bh, t_k, hd), dv (bh, t_k, hd_v). Rows of a hidden key are written as exact zeros. */
 int limn_b200_sdpa_bwd_kv(const void* q, const void* k, const void* v, const void* dout,
@@ -120,6 +132,11 @@ int limn_b200_sdpa_bwd_q_layout(const void* q, const void* k, const void* v, con
                                 void* dq,
                                 int layout, int dtype, int batch, int heads, int t_q, int t_k, int hd, int hd_v,
                                 int causal, double scale, void* stream);
+int limn_b200_sdpa_bwd_q_fused_layout(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                                      const void* lse, const void* key_mask,
+                                      void* dq, void* delta,
+                                      int layout, int dtype, int batch, int heads, int t_q, int t_k, int hd, int hd_v,
+                                      int causal, double scale, void* stream);
 int limn_b200_sdpa_bwd_kv_layout(const void* q, const void* k, const void* v, const void* dout,
                                  const void* lse, const void* delta, const void* key_mask,
                                  void* dk, void* dv,

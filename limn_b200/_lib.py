@@ -26,11 +26,13 @@ LAYOUT_CODES = {"bhtd": 0, "bthd": 1}
 SIGNATURES = {
     "limn_b200_sdpa_fwd": (c_int, (_P, _P, _P, _P, _P, _P) + _SHAPE),
     "limn_b200_sdpa_bwd_q": (c_int, (_P, _P, _P, _P, _P, _P, _P, _P) + _SHAPE),
+    "limn_b200_sdpa_bwd_q_fused": (c_int, (_P, _P, _P, _P, _P, _P, _P, _P, _P) + _SHAPE),
     "limn_b200_sdpa_bwd_kv": (c_int, (_P, _P, _P, _P, _P, _P, _P, _P, _P) + _SHAPE),
     "limn_b200_sdpa_bwd_q_static": (c_int, (_P, _P, _P, _P, _P, _P, _P, _P, _P) + _SHAPE),
     "limn_b200_sdpa_delta": (c_int, (_P, _P, _P, c_int, c_longlong, c_int, _P)),
     "limn_b200_sdpa_fwd_layout": (c_int, (_P, _P, _P, _P, _P, _P) + _LAYOUT_SHAPE),
     "limn_b200_sdpa_bwd_q_layout": (c_int, (_P, _P, _P, _P, _P, _P, _P, _P) + _LAYOUT_SHAPE),
+    "limn_b200_sdpa_bwd_q_fused_layout": (c_int, (_P, _P, _P, _P, _P, _P, _P, _P, _P) + _LAYOUT_SHAPE),
     "limn_b200_sdpa_bwd_kv_layout": (c_int, (_P, _P, _P, _P, _P, _P, _P, _P, _P) + _LAYOUT_SHAPE),
     "limn_b200_sdpa_delta_layout": (c_int, (_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P)),
     "limn_b200_sdpa_path": (c_int, (c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_double)),

@@ -198,7 +198,7 @@ int validate_op(Op op, const char* name, const Problem& p) {
   bool have_rest = true;
   switch (op) {
     case Op::Fwd: have_rest = p.out && p.lse_out; break;
-    case Op::BwdQ: have_rest = p.dout && p.lse_in && p.delta && p.dq; break;
+    case Op::BwdQ: have_rest = p.dout && p.lse_in && p.delta && p.dq && (!p.fuse_delta || p.out); break;
     case Op::BwdKV: have_rest = p.dout && p.lse_in && p.delta && p.dk && p.dv; break;
   }
   if (!have_inputs || !have_rest) return fail(LIMN_B200_BAD_ARGUMENT, "%s: a required pointer is null", name);
@@ -216,6 +216,10 @@ int dispatch_op(Op op, const char* name, const Problem& p) {
   if (int rc = validate_op(op, name, p)) return rc;
   if (p.bh == 0) return LIMN_B200_OK;
   if (tcgen05_serves(op, p)) return tcgen05_launch(op, p);
+  if (op == Op::BwdQ && p.fuse_delta) {
+    // the general kernels read delta: fill it first, as the unfused sequence would
+    if (int rc = general_delta(p.out, p.dout, const_cast<void*>(p.delta), p.dtype, p.bh * p.t_q, p.hd_v, p.stream)) return rc;
+  }
   return general_launch(op, p);
 }
 
@@ -239,6 +243,15 @@ int limn_b200_sdpa_bwd_q(const void* q, const void* k, const void* v, const void
   Problem p = problem(q, k, v, key_mask, dtype, bh, t_q, t_k, hd, hd_v, causal, scale, stream);
   p.dout = dout, p.lse_in = lse, p.delta = delta, p.dq = dq;
   return dispatch_op(Op::BwdQ, "sdpa_bwd_q", p);
+}
+
+int limn_b200_sdpa_bwd_q_fused(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                               const void* lse, const void* key_mask, void* dq, void* delta, int dtype, long long bh,
+                               int t_q, int t_k, int hd, int hd_v, int causal, double scale, void* stream) {
+  Problem p = problem(q, k, v, key_mask, dtype, bh, t_q, t_k, hd, hd_v, causal, scale, stream);
+  p.out = const_cast<void*>(out), p.dout = dout, p.lse_in = lse, p.delta = delta, p.dq = dq;
+  p.fuse_delta = true;
+  return dispatch_op(Op::BwdQ, "sdpa_bwd_q_fused", p);
 }
 
 int limn_b200_sdpa_bwd_kv(const void* q, const void* k, const void* v, const void* dout, const void* lse,
@@ -282,6 +295,18 @@ int limn_b200_sdpa_bwd_q_layout(const void* q, const void* k, const void* v, con
   if (int rc = with_layout("sdpa_bwd_q", p, layout, batch, heads)) return rc;
   p.dout = dout, p.lse_in = lse, p.delta = delta, p.dq = dq;
   return dispatch_op(Op::BwdQ, "sdpa_bwd_q", p);
+}
+
+int limn_b200_sdpa_bwd_q_fused_layout(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                                      const void* lse, const void* key_mask, void* dq, void* delta, int layout, int dtype,
+                                      int batch, int heads, int t_q, int t_k, int hd, int hd_v, int causal, double scale,
+                                      void* stream) {
+  clear_error();
+  Problem p = problem(q, k, v, key_mask, dtype, 0, t_q, t_k, hd, hd_v, causal, scale, stream);
+  if (int rc = with_layout("sdpa_bwd_q_fused", p, layout, batch, heads)) return rc;
+  p.out = const_cast<void*>(out), p.dout = dout, p.lse_in = lse, p.delta = delta, p.dq = dq;
+  p.fuse_delta = true;
+  return dispatch_op(Op::BwdQ, "sdpa_bwd_q_fused", p);
 }
 
 int limn_b200_sdpa_bwd_kv_layout(const void* q, const void* k, const void* v, const void* dout, const void* lse,

@@ -35,6 +35,9 @@ struct Problem {
   // With heads > 0, bh = batch * heads and problem p is (batch p / heads, head p % heads).
   int layout = 0;
   int heads = 0;
+  // dQ pass only: compute delta from `out` (the forward's O) and dO on the way and write it to `delta`, instead of
+  // reading it. Served by the tensor-core kernels; the general family runs the row-dot kernel first.
+  bool fuse_delta = false;
   // Where kernels that wait record giving up. Null means the per-device word status_word() allocates.
   unsigned int* status = nullptr;
   // Two zeroed words for the kernels' work counters. Null means a pair from schedule_words().

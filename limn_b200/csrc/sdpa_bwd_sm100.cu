@@ -119,6 +119,11 @@ struct BwdParams {
   const unsigned short* mask;  // (bh, t_k) key flags in the storage dtype, 0 hides a key; null without a mask
   const float* lse;
   const float* delta;
+  // dQ pass with the row statistic computed on the way (fused entry point): the forward's O and dO as plain
+  // pointers, and where to leave delta for the dK/dV pass. Null otherwise: delta is then an input.
+  const void* o_rows;
+  const void* do_rows;
+  float* delta_out;
   void* out0;   // dQ, or dK
   void* out1;   // dV
   unsigned* status;
@@ -150,6 +155,34 @@ __device__ __forceinline__ void store_row32(void* base, long long elem_offset, c
     }
     dst[v4] = make_uint4(w[0], w[1], w[2], w[3]);
   }
+}
+
+// sum_d a[d] * b[d] over one row of D 16-bit elements each, in fp32 (four partial sums): the delta of one query
+// row from its O and dO rows (limn/tensor.py:705-706).
+template <int D, bool kFp16>
+__device__ __forceinline__ float row_dot(const void* a_row, const void* b_row) {
+  const uint4* a = static_cast<const uint4*>(a_row);
+  const uint4* b = static_cast<const uint4*>(b_row);
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) {
+    const uint4 x = a[i], y = b[i];
+    const uint32_t xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      float x0, x1, y0, y1;
+      if (kFp16) {
+        const float2 fx = __half22float2(*reinterpret_cast<const __half2*>(&xs[w])), fy = __half22float2(*reinterpret_cast<const __half2*>(&ys[w]));
+        x0 = fx.x, x1 = fx.y, y0 = fy.x, y1 = fy.y;
+      } else {
+        x0 = __uint_as_float(xs[w] << 16), x1 = __uint_as_float(xs[w] & 0xffff0000u);
+        y0 = __uint_as_float(ys[w] << 16), y1 = __uint_as_float(ys[w] & 0xffff0000u);
+      }
+      acc[w] = fmaf(x0, y0, acc[w]);
+      acc[w] = fmaf(x1, y1, acc[w]);
+    }
+  }
+  return (acc[0] + acc[1]) + (acc[2] + acc[3]);
 }
 
 // kKV = false: sdpa_bwd_q (CTA owns query rows, streams K/V). kKV = true: sdpa_bwd_kv.
@@ -493,7 +526,8 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         f.d0 = prm.delta[sb + q0], f.d1 = prm.delta[sb + q1];
       } else {
         const int row = min(of.own0 + r, prm.t_q - 1);
-        f.l0 = prm.lse[sb + row], f.d0 = prm.delta[sb + row];
+        f.l0 = prm.lse[sb + row];
+        if (prm.o_rows == nullptr) f.d0 = prm.delta[sb + row];
       }
       return f;
     };
@@ -521,6 +555,15 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     uint64_t row_neg_l2 = 0, row_neg_delta = 0;
     if (!kKV) {
       const bool in = own0 + r < prm.t_q;
+      if (prm.o_rows != nullptr) {
+        // the fused entry point: delta of the own row from the row of O and of dO (both groups compute it, so
+        // that neither waits for the other; group 0 leaves it for the dK/dV pass). The loads run while the
+        // producer fetches the item's tiles and the first scores are computed.
+        const int row = min(own0 + r, prm.t_q - 1);
+        const long long at = (item.batch * prm.out_strides.batch + item.head * prm.out_strides.head + row * prm.out_strides.row) * 2;
+        head.d0 = row_dot<D, kFp16>(static_cast<const unsigned char*>(prm.o_rows) + at, static_cast<const unsigned char*>(prm.do_rows) + at);
+        if (in && group == 0) prm.delta_out[stat_base + row] = head.d0;
+      }
       const float nl = in ? -head.l0 * kLog2e : -INFINITY;
       const float nd = in ? -head.d0 : 0.f;
       row_neg_l2 = f2_pack(nl, nl);
@@ -808,6 +851,9 @@ int launch_bwd(const Problem& p) {
   prm.mask = static_cast<const unsigned short*>(p.mask);
   prm.lse = static_cast<const float*>(p.lse_in);
   prm.delta = static_cast<const float*>(p.delta);
+  prm.o_rows = (!kKV && p.fuse_delta) ? p.out : nullptr;
+  prm.do_rows = (!kKV && p.fuse_delta) ? p.dout : nullptr;
+  prm.delta_out = (!kKV && p.fuse_delta) ? static_cast<float*>(const_cast<void*>(p.delta)) : nullptr;
   prm.out0 = kKV ? p.dk : p.dq;
   prm.out1 = kKV ? p.dv : nullptr;
   prm.heads = heads;

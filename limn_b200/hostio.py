@@ -80,9 +80,7 @@ class HostPipeline:
             self.launches += L.limn_b200_last_launch_count()
             if self.backward:
                 dod = ins[3].ptr
-                self._check(L.limn_b200_sdpa_delta(outs[0].ptr, dod, delta_dev.ptr, self.code, count * t, d, self.run.handle), "row dot")
-                self.launches += L.limn_b200_last_launch_count()
-                self._check(L.limn_b200_sdpa_bwd_q(qd, kd, vd, dod, lse_dev.ptr, delta_dev.ptr, None, outs[1].ptr, *tail), "sdpa_bwd_q")
+                self._check(L.limn_b200_sdpa_bwd_q_fused(qd, kd, vd, outs[0].ptr, dod, lse_dev.ptr, None, outs[1].ptr, delta_dev.ptr, *tail), "sdpa_bwd_q")
                 self.launches += L.limn_b200_last_launch_count()
                 self._check(L.limn_b200_sdpa_bwd_kv(qd, kd, vd, dod, lse_dev.ptr, delta_dev.ptr, None, outs[2].ptr, outs[3].ptr, *tail), "sdpa_bwd_kv")
                 self.launches += L.limn_b200_last_launch_count()

@@ -38,7 +38,7 @@ def test_pipeline_matches_device_resident_calls(backward):
     up, down = pipe(*args, **extra)
     assert up == (4 if backward else 3) * bh * t * d * 2
     assert down == (4 if backward else 1) * bh * t * d * 2 + bh * t * 4
-    assert pipe.launches == (4 if backward else 1) * 3  # three chunks
+    assert pipe.launches == (3 if backward else 1) * 3  # three chunks, the row dot inside the dQ pass
     assert runtime.device_status() == 0
 
     att = host.Attention(host.Device(), q, k, v, causal=True)
@@ -46,5 +46,8 @@ def test_pipeline_matches_device_resident_calls(backward):
     np.testing.assert_array_equal(pinned["out"].array, want_out.view(np.uint16))
     np.testing.assert_array_equal(pinned["lse"].array, want_lse[..., 0])
     if backward:
+        # the pipeline computes the row dot inside the dQ pass, the comparison run as a kernel of its own: the two
+        # sums differ in their last float32 bits, so the gradients agree to a bfloat16 step rather than bit for bit
         for name, want in zip(("dq", "dk", "dv"), att.backward(do)):
-            np.testing.assert_array_equal(pinned[name].array, want.view(np.uint16))
+            got = pinned[name].array.view(BF16).astype(np.float32)
+            np.testing.assert_allclose(got, want.astype(np.float32), rtol=2**-7, atol=2e-3)

@@ -178,6 +178,59 @@ def test_masked_row_without_a_visible_key_on_the_tensor_core_path(dev):
     assert float(np.abs(lse[:, 5:] - want_lse[:, 5:]).max()) <= 1e-3
 
 
+FUSED_CASES = [
+    # id, dtype, code, shape (q = k = v), causal, key mask?, layout
+    ("bf16 d128 causal", BF16, 2, (3, 384, 128), True, False, "bhtd"),
+    ("bf16 d64 full ragged", BF16, 2, (2, 200, 64), False, False, "bhtd"),
+    ("f16 d64 causal masked", np.float16, 1, (4, 300, 64), True, True, "bhtd"),
+    ("bf16 d128 full token-major", BF16, 2, (6, 260, 128), False, False, "bthd"),
+    ("f32 d32 causal (general path)", np.float32, 0, (2, 100, 32), True, False, "bhtd"),
+]
+
+
+@pytest.mark.parametrize("case", FUSED_CASES, ids=[c[0] for c in FUSED_CASES])
+def test_fused_dq_matches_delta_then_dq(case):
+    """limn_b200_sdpa_bwd_q_fused computes the row dot inside the dQ pass and leaves it for the dK/dV pass: its dQ
+    and its delta must be what limn_b200_sdpa_delta followed by limn_b200_sdpa_bwd_q give, and delta the oracle's."""
+    from limn_b200 import runtime
+    from limn_b200._lib import check, lib
+
+    L = lib()
+    _, dtype, code, shape, causal, masked, layout = case
+    bh, t, d = shape
+    rng = np.random.default_rng(bh * 1000 + t)
+    q, k, v, do = (rng.standard_normal(shape).astype(np.float32).astype(dtype) for _ in range(4))
+    dev = [runtime.upload(a) for a in (q, k, v, do)]
+    mask = runtime.upload(np.broadcast_to(np.arange(t) < t * 3 // 4, (bh, t)).astype(np.float32).astype(dtype)) if masked else None
+    m = mask.ptr if mask is not None else None
+    out, lse = runtime.empty(q.nbytes), runtime.empty(bh * t * 4)
+    delta_a, delta_b = runtime.empty(bh * t * 4), runtime.empty(bh * t * 4)
+    dq_a, dq_b = runtime.empty(q.nbytes), runtime.empty(q.nbytes)
+    if layout == "bthd":
+        # the same bytes read as one batch of bh heads held token-major: (1, t, bh, d)
+        tail = (1, code, 1, bh, t, t, d, d, int(causal), d**-0.5, None)
+        check(L.limn_b200_sdpa_fwd_layout(dev[0].ptr, dev[1].ptr, dev[2].ptr, m, out.ptr, lse.ptr, *tail), "sdpa")
+        check(L.limn_b200_sdpa_delta_layout(out.ptr, dev[3].ptr, delta_a.ptr, 1, code, 1, bh, t, d, None), "row dot")
+        check(L.limn_b200_sdpa_bwd_q_layout(dev[0].ptr, dev[1].ptr, dev[2].ptr, dev[3].ptr, lse.ptr, delta_a.ptr, m, dq_a.ptr, *tail), "dq")
+        check(L.limn_b200_sdpa_bwd_q_fused_layout(dev[0].ptr, dev[1].ptr, dev[2].ptr, out.ptr, dev[3].ptr, lse.ptr, m, dq_b.ptr, delta_b.ptr, *tail), "fused dq")
+    else:
+        tail = (code, bh, t, t, d, d, int(causal), d**-0.5, None)
+        check(L.limn_b200_sdpa_fwd(dev[0].ptr, dev[1].ptr, dev[2].ptr, m, out.ptr, lse.ptr, *tail), "sdpa")
+        check(L.limn_b200_sdpa_delta(out.ptr, dev[3].ptr, delta_a.ptr, code, bh * t, d, None), "row dot")
+        check(L.limn_b200_sdpa_bwd_q(dev[0].ptr, dev[1].ptr, dev[2].ptr, dev[3].ptr, lse.ptr, delta_a.ptr, m, dq_a.ptr, *tail), "dq")
+        check(L.limn_b200_sdpa_bwd_q_fused(dev[0].ptr, dev[1].ptr, dev[2].ptr, out.ptr, dev[3].ptr, lse.ptr, m, dq_b.ptr, delta_b.ptr, *tail), "fused dq")
+    assert L.limn_b200_last_launch_count() == (1 if code != 0 else 2)  # the general family still runs the row dot as a kernel
+    assert runtime.device_status() == 0
+    two_step, fused = runtime.download(delta_a, np.float32, (bh, t)), runtime.download(delta_b, np.float32, (bh, t))
+    np.testing.assert_allclose(fused, two_step, rtol=1e-5, atol=1e-5 * float(np.abs(two_step).max()))
+    device_out = runtime.download(out, dtype, (bh, t, d) if layout == "bhtd" else (t, bh, d))
+    do_as_held = do if layout == "bhtd" else do.reshape(t, bh, d)
+    want_delta = oracle.row_delta(do_as_held, device_out)[..., 0]
+    parity(fused, want_delta if layout == "bhtd" else want_delta.T, 1e-5, "fused delta")
+    a, b = widen(runtime.download(dq_a, dtype, shape)), widen(runtime.download(dq_b, dtype, shape))
+    np.testing.assert_allclose(b, a, rtol=2**-7 if code != 0 else 1e-5, atol=2e-3 if code != 0 else 1e-5)
+
+
 def test_two_runs_give_the_same_bits(dev):
     import limn_standin as host
 
