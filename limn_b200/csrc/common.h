@@ -79,6 +79,25 @@ int sm_count(int* count);
 int validate_op(Op op, const char* name, const Problem& p);
 int dispatch_op(Op op, const char* name, const Problem& p);
 
+// Launch with programmatic stream serialization: the kernel may be scheduled while the last CTAs of the kernel
+// before it in the stream are still running, and waits for that kernel itself (ptx::grid_dependency_wait) before
+// it touches global memory. Hides the launch latency and set-up of back-to-back kernels.
+template <typename... Params, typename... Args>
+cudaError_t launch_overlapped(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared_bytes, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = shared_bytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
 // Kernel families. Each returns a status code and enqueues on p.stream.
 int general_launch(Op op, const Problem& p);
 int general_delta(const void* out, const void* dout, void* delta, int dtype, long long rows, int hd_v,

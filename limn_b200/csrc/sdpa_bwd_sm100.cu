@@ -242,7 +242,6 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   };
 
   if (threadIdx.x == 0) {
-    abort_flag = *reinterpret_cast<volatile unsigned*>(prm.status) != kStatusOk;
     for (int i = 0; i < B::count; ++i) {
       uint32_t arrivals = 1u;
       if (kSeq) {
@@ -259,6 +258,10 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
     mbar_init_fence();
   }
+  // up to here nothing has touched global memory, so all of it may run under the tail of the kernel before this one
+  grid_dependency_wait();
+  grid_launch_dependents();
+  if (threadIdx.x == 0) abort_flag = *reinterpret_cast<volatile unsigned*>(prm.status) != kStatusOk;
   __syncthreads();
   if (warp == kMmaWarp && !abort_flag) {
     tmem_alloc(smem_addr(&tmem_slot), kTmemCols);
@@ -891,8 +894,8 @@ int launch_bwd(const Problem& p) {
               "sizing shared memory for an sdpa backward kernel");
     sized[device] = true;
   }
-  kernel<<<dim3(static_cast<unsigned>(ctas)), dim3(kThreads), L::kBytes, p.stream>>>(map_q, map_k, map_v, map_do, prm);
-  LIMN_CUDA(cudaGetLastError(), "launching an sdpa backward kernel");
+  LIMN_CUDA(launch_overlapped(kernel, dim3(static_cast<unsigned>(ctas)), dim3(kThreads), L::kBytes, p.stream, map_q, map_k, map_v, map_do, prm),
+            "launching an sdpa backward kernel");
   note_launches(1);
   return LIMN_B200_OK;
 }

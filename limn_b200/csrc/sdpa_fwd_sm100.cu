@@ -170,7 +170,6 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
   // ---- set-up: barriers, tensor memory ----
   if (threadIdx.x == 0) {
-    abort_flag = *reinterpret_cast<volatile unsigned*>(prm.status) != kStatusOk;
     for (int i = 0; i < B::count; ++i) {
       unsigned arrivals = 1u;
       if ((i >= B::p_full && i < B::p_full + 2) || (i >= B::p_half && i < B::p_half + 2) || (i >= B::o_free && i < B::o_free + 2))
@@ -180,6 +179,10 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
     mbar_init_fence();
   }
+  // up to here nothing has touched global memory, so all of it may run under the tail of the kernel before this one
+  grid_dependency_wait();
+  grid_launch_dependents();
+  if (threadIdx.x == 0) abort_flag = *reinterpret_cast<volatile unsigned*>(prm.status) != kStatusOk;
   __syncthreads();
   if (warp == kMmaWarp && !abort_flag) {
     tmem_alloc(smem_addr(&tmem_slot), kTmemCols);
@@ -622,8 +625,8 @@ int launch_fwd(const Problem& p) {
               "sizing shared memory for the sdpa kernel");
     sized[device] = true;
   }
-  kernel<<<dim3(static_cast<unsigned>(ctas)), dim3(kThreads), L::kBytes, p.stream>>>(map_q, map_k, map_v, prm);
-  LIMN_CUDA(cudaGetLastError(), "launching the sdpa kernel");
+  LIMN_CUDA(launch_overlapped(kernel, dim3(static_cast<unsigned>(ctas)), dim3(kThreads), L::kBytes, p.stream, map_q, map_k, map_v, prm),
+            "launching the sdpa kernel");
   note_launches(1);
   return LIMN_B200_OK;
 }

@@ -92,6 +92,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
   return mbar_wait_for(bar, parity, status, tag, kWaitBudgetTicks);
 }
 
+// ---- programmatic dependent launch ----
+// A kernel launched with the programmatic-serialization attribute may start while the kernel before it in the
+// stream is still running its last CTAs; grid_dependency_wait() is where it then waits until that kernel has
+// finished and its writes are visible (a no-op when the kernel was launched the ordinary way). Nothing that
+// reads or writes global memory may come before it. grid_launch_dependents() tells the scheduler that the
+// kernel after this one may begin the same way as soon as this one's CTAs make room.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- fences ----
 __device__ __forceinline__ void fence_async_shared() {
   // generic-proxy writes to shared memory -> visible to the async proxy (TMA store, MMA operands)
