@@ -127,10 +127,29 @@ def build_sdpa_bwd_kv(node: Any) -> Runner:
     return run
 
 
+def build_sdpa_bwd_q_fused(node: Any) -> Runner:
+    """Runner for "sdpa_bwd_q_fused": inputs (q, k, v, O, dO, L[, mask]) -> outs (dQ, delta). Not one of limn's
+    names: the node only exists once limn_b200.frontend.fuse_row_dot() has taught the frontend to build it in
+    place of its row-dot reduce followed by "sdpa_bwd_q" (limn/tensor.py:702-710)."""
+    form = Form(node, 6)
+    fn = lib().limn_b200_sdpa_bwd_q_fused
+    tail = form.tail()
+
+    def run(inputs: list[Any], outs: list[Any]) -> None:
+        ins, (dq, delta) = _pointers(form, inputs, outs)
+        mask = ins[6] if form.has_mask else None
+        check(fn(ins[0], ins[1], ins[2], ins[3], ins[4], ins[5], mask, dq, delta, *tail), "launching sdpa_bwd_q_fused")
+        _note_launch()
+
+    return run
+
+
+SDPA_BWD_Q_FUSED = "sdpa_bwd_q_fused"
 BUILDERS: dict[str, Callable[[Any], Runner]] = {
     SDPA: build_sdpa,
     SDPA_BWD_Q: build_sdpa_bwd_q,
     SDPA_BWD_KV: build_sdpa_bwd_kv,
+    SDPA_BWD_Q_FUSED: build_sdpa_bwd_q_fused,
 }
 
 
@@ -167,8 +186,9 @@ def check_device_status(doing: str = "waiting for the batch") -> None:
 
 
 def install(device: Any) -> Any:
-    """Register the three builders on a device that has a `custom` registry (limn's
-    CompiledDevice, limn/jit.py:103-135). Loads the shared library first, so a missing or
+    """Register the builders on a device that has a `custom` registry (limn's CompiledDevice,
+    limn/jit.py:103-135): limn's three names, and "sdpa_bwd_q_fused", which limn's frontend only asks
+    for after limn_b200.frontend.fuse_row_dot(). Loads the shared library first, so a missing or
     unloadable library fails here rather than at the first step.
 
     The device's finish() (limn's one synchronise per batch, limn/jit.py:183) is wrapped so that

@@ -132,7 +132,7 @@ def test_install_needs_a_registry():
             self.custom = {}
 
     dev = limn_b200.install(WithRegistry())
-    assert set(dev.custom) == {"sdpa", "sdpa_bwd_q", "sdpa_bwd_kv"}
+    assert set(dev.custom) == {"sdpa", "sdpa_bwd_q", "sdpa_bwd_kv", "sdpa_bwd_q_fused"}
 
 
 def test_installed_finish_reports_a_kernel_that_gave_up(monkeypatch):
@@ -235,3 +235,55 @@ def test_install_into_limns_own_registry_and_plan():
         device_module.set_device("numpy")
         if "original" in locals():
             device_module.DEVICES["c"] = original
+
+
+@pytest.mark.skipif(not (REFERENCE / "limn").is_dir(), reason="the reference checkout is not on this machine")
+def test_the_frontend_patch_swaps_the_row_dot_for_the_fused_op():
+    """limn_b200.frontend.fuse_row_dot(): on a device with "sdpa_bwd_q_fused" the backward graph holds the fused
+    node (dQ, delta) feeding "sdpa_bwd_kv" and no row-dot reduce; on limn's numpy device, which has no such
+    kernel, the graph is limn's own; undo() restores limn's function. Graph level only, nothing is launched."""
+    sys.path.insert(0, str(REFERENCE))
+    try:
+        import limn
+        import limn.device as device_module
+        import limn.tensor as frontend
+        from limn import backend_c
+        from limn.ops import Op, topological
+
+        import limn_b200
+        from limn_b200 import frontend as patch
+
+        def backward_nodes():
+            rng = np.random.default_rng(0)
+            q, k, v = (limn.Tensor(rng.standard_normal((2, 3, 64, 16)).astype(np.float32), requires_grad=True) for _ in range(3))
+            out = q.attention(k, v, causal=True)
+            grads = limn.grad((out * out).sum(), [q, k, v])
+            return topological([g.node for g in grads])
+
+        before = frontend._attention_backward
+        undo = patch.fuse_row_dot()
+        try:
+            assert patch.fuse_row_dot() is not None  # patching twice is harmless
+            names = [n.arg.name for n in backward_nodes() if n.op is Op.CUSTOM]  # numpy device: limn's own graph
+            assert "sdpa_bwd_q_fused" not in names and "sdpa_bwd_q" in names
+            dev = limn_b200.install(backend_c.CDevice())
+            original = device_module.DEVICES["c"]
+            device_module.DEVICES["c"] = lambda: dev
+            try:
+                limn.set_device("c")
+                nodes = backward_nodes()
+            finally:
+                device_module.DEVICES["c"] = original
+                limn.set_device("numpy")
+            customs = [n for n in nodes if n.op is Op.CUSTOM]
+            assert {n.arg.name for n in customs} == {"sdpa", "sdpa_bwd_q_fused", "sdpa_bwd_kv"}
+            fused = [n for n in customs if n.arg.name == "sdpa_bwd_q_fused"]
+            assert sorted(n.arg.index for n in fused) == [0, 1] and len(fused[0].srcs) == 6
+            kv = next(n for n in customs if n.arg.name == "sdpa_bwd_kv")
+            assert kv.srcs[5] in fused and kv.srcs[5].arg.index == 1, "the dK/dV op reads the delta the fused op wrote"
+            assert not any(n.op is Op.SUM and n.shape[-1] == 1 and len(n.shape) == 4 for n in nodes), "the row-dot reduce is gone"
+        finally:
+            undo()
+        assert frontend._attention_backward is before
+    finally:
+        sys.path.remove(str(REFERENCE))

@@ -234,6 +234,53 @@ def test_capture_replays_against_new_buffers(limn, cudev):
         limn.device.set_device("numpy")
 
 
+def test_the_frontend_patch_for_the_fused_row_dot(limn):
+    """limn_b200.frontend.fuse_row_dot(): with the cuda device active, limn's autograd then builds
+    "sdpa_bwd_q_fused" -> (dQ, delta) in place of its row-dot reduce and "sdpa_bwd_q". The gradients match limn's
+    numpy device (whose graph stays limn's own: it has no such kernel) and the unpatched cuda run, and the plan is
+    a call shorter."""
+    from limn.ops import Op, topological
+
+    import limn_b200
+    from limn_b200 import frontend as patch
+
+    shape = (2, 2, 256, 64)
+    data = [rng.standard_normal(shape).astype(np.float32) for _ in range(4)]
+
+    def grads_on(device_name: str):
+        limn.device.set_device(device_name)
+        try:
+            dev = limn.device.active()
+            if device_name == "cuda":
+                limn_b200.install(dev)
+            q, k, v = (limn.Tensor(d, dtype=limn.bfloat16, requires_grad=True) for d in data[:3])
+            out = q.attention(k, v, causal=True)
+            grads = limn.grad((out * limn.Tensor(data[3], dtype=limn.bfloat16)).sum(), [q, k, v])
+            names = [n.arg.name for n in topological([g.node for g in grads]) if n.op is Op.CUSTOM]
+            calls = None
+            if device_name == "cuda":
+                limn.realize(*grads)
+                calls = max(len(plan.calls) for plan in dev.plans.values())
+            return [g.numpy().astype(np.float32) for g in grads], names, calls
+        finally:
+            limn.device.set_device("numpy")
+
+    want, _, _ = grads_on("numpy")
+    plain, plain_names, plain_calls = grads_on("cuda")
+    undo = patch.fuse_row_dot()
+    try:
+        on_numpy, numpy_names, _ = grads_on("numpy")
+        fused, fused_names, fused_calls = grads_on("cuda")
+    finally:
+        undo()
+    assert "sdpa_bwd_q_fused" in fused_names and "sdpa_bwd_q" not in fused_names
+    assert "sdpa_bwd_q_fused" not in plain_names and "sdpa_bwd_q_fused" not in numpy_names
+    assert fused_calls < plain_calls, (fused_calls, plain_calls)
+    for got in (plain, fused, on_numpy):
+        for g, w in zip(got, want, strict=True):
+            np.testing.assert_allclose(g, w, rtol=3e-2, atol=3e-2)
+
+
 def test_a_gpt_training_step_under_capture(limn):
     """The caller of the GPT attention layer: a two-layer byte-level GPT step shaped like limn's
     examples/train_stories.py (its model and step, :26-56 and :140-147 there) with bfloat16 attention operands,
