@@ -177,6 +177,26 @@ int limn_b200_device_status(unsigned int* status);
  * making any production kernel misbehave and without hanging or faulting anything. */
 int limn_b200_wait_probe(long long budget_ticks, unsigned int* gave_up, void* stream);
 
+/* ---- the gather of (batch, head) shards over NCCL, for sharded hosts without a communication library of their own ----
+ * No counterpart in the reference, which is single-GPU (limn/backend_cuda.py:283 takes device 0). The problems of a
+ * batch are independent: rank r of N computes problems [r BH/N, (r+1) BH/N) with the entry points above and no
+ * communication, and the outputs are then gathered into one tensor on every GPU. One process per GPU, one
+ * communicator per process; NCCL (libnccl.so.2, or the file LIMN_B200_NCCL_LIBRARY names) is loaded when the first of
+ * these is called, so a single-GPU host never needs it. Failures come back as status codes with a message, never as
+ * an abort: LIMN_B200_UNSUPPORTED when NCCL cannot be loaded, LIMN_B200_BAD_ARGUMENT for a misuse,
+ * LIMN_B200_CUDA_ERROR with NCCL's own error string otherwise.
+ *   limn_b200_nccl_unique_id: rank 0 fills LIMN_B200_NCCL_ID_BYTES bytes (host memory); the host carries them to the
+ *     other ranks by whatever means it has (a file, a socket, its launcher).
+ *   limn_b200_nccl_init: every rank, with its own device current, the same id and world size.
+ *   limn_b200_nccl_all_gather: recv (world * bytes_per_rank bytes) receives every rank's send (bytes_per_rank bytes) in
+ *     rank order, enqueued on `stream`; send may be the rank's own slice of recv.
+ *   limn_b200_nccl_destroy: releases the communicator. */
+#define LIMN_B200_NCCL_ID_BYTES 128
+int limn_b200_nccl_unique_id(void* id_out);
+int limn_b200_nccl_init(int rank, int world, const void* id);
+int limn_b200_nccl_all_gather(const void* send, void* recv, unsigned long long bytes_per_rank, void* stream);
+int limn_b200_nccl_destroy(void);
+
 /* ---- plumbing for hosts without a CUDA binding of their own (tests, benchmark) ----
  * limn itself allocates and copies through the driver API (limn/backend_cuda.py:297-326)
  * and never calls these. */

@@ -41,6 +41,10 @@ SIGNATURES = {
     "limn_b200_version": (c_int, ()),
     "limn_b200_device_status": (c_int, (POINTER(c_uint),)),
     "limn_b200_wait_probe": (c_int, (c_longlong, _P, _P)),
+    "limn_b200_nccl_unique_id": (c_int, (_P,)),
+    "limn_b200_nccl_init": (c_int, (c_int, c_int, _P)),
+    "limn_b200_nccl_all_gather": (c_int, (_P, _P, c_ulonglong, _P)),
+    "limn_b200_nccl_destroy": (c_int, ()),
     "limn_b200_device_count": (c_int, (POINTER(c_int),)),
     "limn_b200_set_device": (c_int, (c_int,)),
     "limn_b200_mem_alloc": (c_int, (POINTER(c_void_p), c_ulonglong)),

@@ -21,7 +21,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OBJ = HERE / "build"
 LIB = HERE / "liblimn_b200.so"
-SOURCES = ["capi.cu", "sdpa_general.cu", "dispatch_sm100.cu", "sdpa_fwd_sm100.cu", "sdpa_bwd_sm100.cu", "static_scratch.cu", "wait_probe.cu"]
+SOURCES = ["capi.cu", "sdpa_general.cu", "dispatch_sm100.cu", "sdpa_fwd_sm100.cu", "sdpa_bwd_sm100.cu", "static_scratch.cu", "wait_probe.cu", "nccl_gather.cpp"]
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC", "-Xptxas", "-v",
@@ -62,7 +62,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     (OBJ / "ptxas.log").write_text("\n".join(log for _, log in results))
     if verbose:
         print("\n".join(log for _, log in results))
-    link = [nvcc(), "-shared", "-o", str(LIB), *[obj for obj, _ in results], "-cudart", "static"]
+    link = [nvcc(), "-shared", "-o", str(LIB), *[obj for obj, _ in results], "-cudart", "static", "-ldl"]
     done = subprocess.run(link, capture_output=True, text=True)
     if done.returncode != 0:
         raise RuntimeError(f"linking liblimn_b200.so failed:\n{done.stdout}\n{done.stderr}")

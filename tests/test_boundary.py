@@ -59,6 +59,34 @@ def test_argument_checks_answer_without_a_device():
     assert lib().limn_b200_sdpa_delta_layout(one, one, one, 5, 2, 1, 2, 4, 64, None) == 1 and "layout" in err()
 
 
+def test_nccl_entry_points_fail_with_codes_not_aborts(monkeypatch):
+    """The sharded path's failure handling, host side only: misuse and a communication library that cannot be
+    loaded come back as status codes with a message."""
+    import ctypes
+
+    from limn_b200._lib import BAD_ARGUMENT, UNSUPPORTED, last_error, lib
+
+    L = lib()
+    buf = ctypes.create_string_buffer(128)
+    assert L.limn_b200_nccl_init(2, 2, buf) == BAD_ARGUMENT and "not one of 2 ranks" in last_error()
+    assert L.limn_b200_nccl_init(0, 2, None) == BAD_ARGUMENT
+    assert L.limn_b200_nccl_all_gather(1, 1, 16, None) == BAD_ARGUMENT and "no communicator" in last_error()
+    assert L.limn_b200_nccl_unique_id(None) == BAD_ARGUMENT
+    assert L.limn_b200_nccl_destroy() == 0  # nothing to destroy is not an error
+
+
+def test_a_missing_nccl_is_reported(tmp_path):
+    """In a process of its own (the library is loaded once per process): a named NCCL that does not exist."""
+    import subprocess
+
+    code = ("import ctypes, sys; sys.path.insert(0, %r); from limn_b200._lib import lib, last_error; "
+            "rc = lib().limn_b200_nccl_unique_id(ctypes.create_string_buffer(128)); print(rc, last_error())") % str(ROOT)
+    done = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, LIMN_B200_NCCL_LIBRARY=str(tmp_path / "libnccl.so.2")),
+                          capture_output=True, text=True, timeout=120)
+    assert done.returncode == 0, done.stderr
+    assert done.stdout.startswith("2 nccl: cannot load"), done.stdout
+
+
 def test_dispatch_policy():
     from limn_b200._lib import PATH_GENERAL, PATH_TCGEN05, lib
 
