@@ -100,7 +100,9 @@ struct BwdBars {
   static constexpr int held_empty = acc_free + 1;   // the item's last scores are computed: the resident tiles may be replaced
   static constexpr int work_full = held_empty + 1;  // + slot: the producer has fetched a work item
   static constexpr int work_empty = work_full + 2;  // + slot: every consumer has read it
-  static constexpr int count = work_empty + 2;
+  static constexpr int delta_full = work_empty + 2;   // + slot, fused dQ pass: the item's row statistics are in shared memory (64 arrivals)
+  static constexpr int delta_empty = delta_full + 2;  // + slot: the elementwise threads have taken them (256 arrivals)
+  static constexpr int count = delta_empty + 2;
 };
 
 // Build-time diagnostic (-DLIMN_TRACE): one CTA records clock64() at each step of its pipeline into a
@@ -203,6 +205,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   __shared__ uint32_t tmem_slot;
   __shared__ uint32_t abort_flag;
   __shared__ unsigned work_ring[2];
+  __shared__ float delta_ring[2][kTile];  // fused dQ pass: delta of the item's 128 query rows, two items deep
 
   const uint32_t base = (smem_addr(smem_unaligned) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_unaligned + (base - smem_addr(smem_unaligned));
@@ -253,7 +256,10 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (i == B::s_full + 1 || i == B::ds_full) arrivals = 256u;
       }
       if (i == B::acc_free) arrivals = 256u;
-      if (i == B::work_empty || i == B::work_empty + 1) arrivals = 9u;  // the MMA warp and the eight elementwise warps
+      // the MMA warp and the eight elementwise warps, and in the fused dQ pass the two warps that compute delta
+      if (i == B::work_empty || i == B::work_empty + 1) arrivals = (!kKV && prm.o_rows != nullptr) ? 11u : 9u;
+      if (i == B::delta_full || i == B::delta_full + 1) arrivals = 64u;    // every thread of the two warps that wrote them
+      if (i == B::delta_empty || i == B::delta_empty + 1) arrivals = 256u;  // every elementwise thread, having read its own
       mbar_init(bar(i), arrivals);
     }
     mbar_init_fence();
@@ -530,7 +536,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       } else {
         const int row = min(of.own0 + r, prm.t_q - 1);
         f.l0 = prm.lse[sb + row];
-        if (prm.o_rows == nullptr) f.d0 = prm.delta[sb + row];
+        if (prm.o_rows == nullptr) f.d0 = prm.delta[sb + row];  // (the fused pass takes delta from shared memory when the item starts)
       }
       return f;
     };
@@ -559,13 +565,12 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     if (!kKV) {
       const bool in = own0 + r < prm.t_q;
       if (prm.o_rows != nullptr) {
-        // the fused entry point: delta of the own row from the row of O and of dO (both groups compute it, so
-        // that neither waits for the other; group 0 leaves it for the dK/dV pass). The loads run while the
-        // producer fetches the item's tiles and the first scores are computed.
-        const int row = min(own0 + r, prm.t_q - 1);
-        const long long at = (item.batch * prm.out_strides.batch + item.head * prm.out_strides.head + row * prm.out_strides.row) * 2;
-        head.d0 = row_dot<D, kFp16>(static_cast<const unsigned char*>(prm.o_rows) + at, static_cast<const unsigned char*>(prm.do_rows) + at);
-        if (in && group == 0) prm.delta_out[stat_base + row] = head.d0;
+        // the fused entry point: warps 10 and 11 computed the item's row statistics when the item was published
+        const unsigned slot = n_item & 1u;
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(B::delta_full + slot), (n_item >> 1) & 1u, prm.status, 0x1340u | slot));
+        if (!ok) break;
+        head.d0 = *reinterpret_cast<volatile float*>(&delta_ring[slot][r]);
+        mbar_arrive(bar(B::delta_empty + slot));
       }
       const float nl = in ? -head.l0 * kLog2e : -INFINITY;
       const float nd = in ? -head.d0 : 0.f;
@@ -818,6 +823,36 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     done += count;
     index = upcoming, item = upcoming_item, head = upcoming_head;
     }  // items
+  }
+
+  else if (!kKV && prm.o_rows != nullptr) {
+    // ================= fused dQ pass: the row statistic delta = sum_d dO * O, by the two spare warps =================
+    // They follow the producer's work ring like every other consumer and so learn of an item while the item
+    // before it is still being computed: by the time the elementwise warps start on it, its 128 statistics lie in
+    // shared memory (and in the caller's delta buffer, for the dK/dV pass). Thread j of the 64 takes rows j and j + 64.
+    const int j = threadIdx.x - (kMmaWarp + 1) * 32;
+    for (unsigned n_item = 0; ok; ++n_item) {
+      unsigned index;
+      ok = __all_sync(0xffffffffu, next_item(n_item, index));
+      if (!ok) break;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B::work_empty + (n_item & 1u)));
+      if (index >= prm.items) break;
+      const Item item = decode(index);
+      const unsigned slot = n_item & 1u;
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(B::delta_empty + slot), ((n_item >> 1) & 1u) ^ 1u, prm.status, 0x1500u | slot));
+      if (!ok) break;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int local = j + 64 * half;
+        const int row = min(item.own0 + local, prm.t_q - 1);
+        const long long at = (item.batch * prm.out_strides.batch + item.head * prm.out_strides.head + row * prm.out_strides.row) * 2;
+        const float d = row_dot<D, kFp16>(static_cast<const unsigned char*>(prm.o_rows) + at, static_cast<const unsigned char*>(prm.do_rows) + at);
+        delta_ring[slot][local] = d;
+        if (item.own0 + local < prm.t_q) prm.delta_out[static_cast<long long>(item.problem) * prm.t_q + row] = d;
+      }
+      mbar_arrive(bar(B::delta_full + slot));  // every writer arrives for itself: the arrival orders its writes before it
+    }
   }
 
   // ---- teardown ----
