@@ -510,6 +510,44 @@ def other_workloads(args, main: str, world: int, rank: int, torch, device, barri
     return found
 
 
+def decode_cases(args, world: int, torch, device, barrier, max_over_ranks) -> dict:
+    """The step of a kv cache (one query row against every key so far), which is not a BASELINE configuration but
+    is the other shape the ops are called in: bound by reading K and V once, so reported against the measured copy
+    bandwidth. Values are random; parity of the shape is tests/test_sdpa_gpu.py's business."""
+    from limn_b200._lib import lib
+
+    L = lib()
+    peak, _ = peaks()
+    hbm_peak = float(peak.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
+    found = {}
+    for name, bh_all, t_k, d in (("one_row_4096_keys_d128", 256, 4096, 128), ("one_row_2048_keys_d64", 1024, 2048, 64)):
+        bh = bh_all // world
+        q = torch.randn((bh, 1, d), device=device).to(torch.bfloat16)
+        k, v = (torch.randn((bh, t_k, d), device=device).to(torch.bfloat16) for _ in range(2))
+        out = torch.empty_like(q)
+        lse = torch.empty((bh, 1), dtype=torch.float32, device=device)
+        torch.cuda.synchronize()
+
+        def launch():
+            code = L.limn_b200_sdpa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), None, out.data_ptr(), lse.data_ptr(), 2, bh, 1, t_k, d, d, 0, d ** -0.5, None)
+            if code:
+                raise RuntimeError(L.limn_b200_last_error().decode())
+
+        for _ in range(3):
+            launch()
+        trials = []
+        for _ in range(3):
+            barrier()
+            time.sleep(args.rest_seconds)
+            barrier()
+            trials.append(max_over_ranks(timed(None, 20, launch)) / 20)
+        ms = min(trials)
+        moved = bh * (2 * t_k * d * 2 + 2 * d * 2 + 4)
+        found[name] = {"problems_per_rank": bh, "ms": ms, "hbm_gbs": moved / (ms * 1e-3) / 1e9, "frac_of_measured_hbm": moved / (ms * 1e-3) / 1e9 / hbm_peak,
+                       "bytes_per_launch": moved}
+    return found
+
+
 def errors(got: np.ndarray, want: np.ndarray) -> dict:
     """Both measures of one comparison: the raw max-abs error and the reference checker's, relative to
     max(1, max |want|) (limn/sdpa.py:251-259)."""
@@ -674,6 +712,8 @@ def gpu_arm(args) -> None:
         del stage
 
     others = other_workloads(args, workload, world, rank, torch, device, barrier, max_over_ranks) if args.others else None
+    if others is not None:
+        others["decode"] = decode_cases(args, world, torch, device, barrier, max_over_ranks)
 
     status = runtime.device_status()
     if status:

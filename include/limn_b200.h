@@ -40,7 +40,9 @@ enum limn_b200_status {
 /* Which kernel family served (or would serve) a problem. */
 enum limn_b200_path {
   LIMN_B200_PATH_GENERAL = 0,  /* SIMT kernels: any float dtype, any hd/hd_v */
-  LIMN_B200_PATH_TCGEN05 = 1   /* TMA + tcgen05 kernels: f16/bf16, hd == hd_v in {64, 128}, any t_q/t_k, with or without key mask */
+  LIMN_B200_PATH_TCGEN05 = 1,  /* TMA + tcgen05 kernels: f16/bf16, hd == hd_v in {64, 128}, any t_q/t_k, with or without key mask */
+  LIMN_B200_PATH_DECODE = 2    /* forward only: f16/bf16, hd == hd_v in {64, 128}, t_q <= 4 without a causal mask (the step of a
+                                  kv cache): one CTA streams a problem's keys and values once, bound by HBM, no tensor cores */
 };
 
 /* "sdpa": replaces emit_sdpa (limn/cuda_emit.py:921-965); oracle limn/sdpa.py:91-137.

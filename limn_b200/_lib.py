@@ -14,7 +14,7 @@ LIB_PATH = Path(__file__).resolve().parent / "liblimn_b200.so"
 
 # dtype codes of enum limn_b200_dtype, by the names limn's DType carries (limn/ops.py:24-27)
 DTYPE_CODES = {"float32": 0, "float16": 1, "bfloat16": 2, "float64": 3}
-PATH_GENERAL, PATH_TCGEN05 = 0, 1
+PATH_GENERAL, PATH_TCGEN05, PATH_DECODE = 0, 1, 2
 OK, BAD_ARGUMENT, UNSUPPORTED, CUDA_ERROR, DEVICE_TIMEOUT = 0, 1, 2, 3, 4  # enum limn_b200_status
 
 _P = c_void_p

@@ -215,6 +215,7 @@ int dispatch_op(Op op, const char* name, const Problem& p) {
   g_launches = 0;
   if (int rc = validate_op(op, name, p)) return rc;
   if (p.bh == 0) return LIMN_B200_OK;
+  if (decode_serves(op, p)) return decode_launch(p);
   if (tcgen05_serves(op, p)) return tcgen05_launch(op, p);
   if (op == Op::BwdQ && p.fuse_delta) {
     // the general kernels read delta: fill it first, as the unfused sequence would
@@ -349,10 +350,11 @@ int limn_b200_sdpa_delta(const void* out, const void* dout, void* delta, int dty
 int limn_b200_sdpa_path(int dtype, long long bh, int t_q, int t_k, int hd, int hd_v, int causal, int has_mask,
                         double scale) {
   clear_error();
-  static const int placeholder = 0;
-  Problem p = problem(&placeholder, &placeholder, &placeholder, has_mask ? &placeholder : nullptr, dtype, bh, t_q, t_k,
+  alignas(16) static const int placeholder[4] = {0, 0, 0, 0};
+  Problem p = problem(placeholder, placeholder, placeholder, has_mask ? placeholder : nullptr, dtype, bh, t_q, t_k,
                       hd, hd_v, causal, scale, nullptr);
   if (check_problem("sdpa", p) != LIMN_B200_OK) return -1;
+  if (decode_serves(Op::Fwd, p)) return LIMN_B200_PATH_DECODE;
   return tcgen05_serves(Op::Fwd, p) ? LIMN_B200_PATH_TCGEN05 : LIMN_B200_PATH_GENERAL;
 }
 

@@ -106,5 +106,8 @@ int general_delta_bthd(const void* out, const void* dout, void* delta, int dtype
                        cudaStream_t stream);
 bool tcgen05_serves(Op op, const Problem& p);
 int tcgen05_launch(Op op, const Problem& p);
+// The forward for decode shapes (a few query rows against many keys): bandwidth-bound, no tensor cores.
+bool decode_serves(Op op, const Problem& p);
+int decode_launch(const Problem& p);
 
 }  // namespace limn_b200

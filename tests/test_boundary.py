@@ -94,7 +94,7 @@ def test_dispatch_policy():
     # dtype codes: f32 0, f16 1, bf16 2, f64 3
     assert path(2, 256, 4096, 4096, 128, 128, 1, 0, 128**-0.5) == PATH_TCGEN05
     assert path(1, 256, 2048, 2048, 64, 64, 0, 0, 0.125) == PATH_TCGEN05
-    assert path(2, 1, 1, 300, 64, 64, 0, 0, 0.125) == PATH_TCGEN05
+    assert path(2, 1, 1, 300, 64, 64, 0, 0, 0.125) == 2  # PATH_DECODE: one query row against many keys
     assert path(2, 2, 64, 64, 64, 64, 0, 1, 0.125) == PATH_TCGEN05  # key mask, 16-bit storage
     for general in (
         (0, 2, 128, 128, 32, 32, 1, 0, 32**-0.5),  # float32 computes at its own width

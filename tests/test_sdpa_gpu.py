@@ -231,6 +231,62 @@ def test_fused_dq_matches_delta_then_dq(case):
     np.testing.assert_allclose(b, a, rtol=2**-7 if code != 0 else 1e-5, atol=2e-3 if code != 0 else 1e-5)
 
 
+DECODE_CASES = [
+    # id, dtype, code, bh, t_q, t_k, d, key mask kind, layout
+    ("bf16 d128 one row 4096 keys", BF16, 2, 24, 1, 4096, 128, None, "bhtd"),
+    ("bf16 d64 one row ragged 1000", BF16, 2, 7, 1, 1000, 64, None, "bhtd"),
+    ("f16 d128 four rows 300 keys", np.float16, 1, 5, 4, 300, 128, None, "bhtd"),
+    ("f16 d64 three rows, padded cache", np.float16, 1, 6, 3, 515, 64, "pad", "bhtd"),
+    ("bf16 d128 two rows, holes", BF16, 2, 4, 2, 777, 128, "holes", "bhtd"),
+    ("bf16 d64 one row, token-major", BF16, 2, 12, 1, 640, 64, None, "bthd"),
+    ("bf16 d128 one row, 3 keys", BF16, 2, 3, 1, 3, 128, None, "bhtd"),
+]
+
+
+@pytest.mark.parametrize("case", DECODE_CASES, ids=[c[0] for c in DECODE_CASES])
+def test_decode_shapes_on_the_streaming_kernel(case):
+    """A few query rows against many keys (the step of a kv cache; the reference's own test of the shape is
+    tests/test_attention.py:385-396 there): served by the bandwidth-bound decode kernel, checked against the oracle,
+    twice for the bits."""
+    from limn_b200 import runtime
+    from limn_b200._lib import PATH_DECODE, check, lib
+
+    L = lib()
+    _, dtype, code, bh, t_q, t_k, d, mask_kind, layout = case
+    assert L.limn_b200_sdpa_path(code, bh, t_q, t_k, d, d, 0, int(mask_kind is not None), d**-0.5) == PATH_DECODE
+    rng = np.random.default_rng(bh * 100 + t_k)
+    q = rng.standard_normal((bh, t_q, d)).astype(np.float32).astype(dtype)
+    k, v = (rng.standard_normal((bh, t_k, d)).astype(np.float32).astype(dtype) for _ in range(2))
+    mask = None
+    if mask_kind == "pad":
+        mask = np.broadcast_to(np.arange(t_k) < t_k * 2 // 3, (bh, t_k)).astype(np.float32).astype(dtype)
+    elif mask_kind == "holes":
+        mask = (rng.random((bh, t_k)) > 0.4).astype(np.float32).astype(dtype)
+        mask[-1] = 0  # the last problem sees no key at all: NaN rows, L = -inf
+    held = [np.ascontiguousarray(a if layout == "bhtd" else a.transpose(1, 0, 2)) for a in (q, k, v)]  # (t, bh, d) = one batch of bh heads
+    dev = [runtime.upload(a) for a in held]
+    mask_dev = runtime.upload(mask) if mask is not None else None
+    results = []
+    for _ in range(2):
+        out, lse = runtime.empty(q.nbytes), runtime.empty(bh * t_q * 4)
+        m = mask_dev.ptr if mask_dev is not None else None
+        if layout == "bthd":
+            check(L.limn_b200_sdpa_fwd_layout(dev[0].ptr, dev[1].ptr, dev[2].ptr, m, out.ptr, lse.ptr, 1, code, 1, bh, t_q, t_k, d, d, 0, d**-0.5, None), "sdpa")
+        else:
+            check(L.limn_b200_sdpa_fwd(dev[0].ptr, dev[1].ptr, dev[2].ptr, m, out.ptr, lse.ptr, code, bh, t_q, t_k, d, d, 0, d**-0.5, None), "sdpa")
+        got = runtime.download(out, dtype, (bh, t_q, d) if layout == "bhtd" else (t_q, bh, d))
+        results.append((got if layout == "bhtd" else got.transpose(1, 0, 2), runtime.download(lse, np.float32, (bh, t_q, 1))))
+    assert runtime.device_status() == 0
+    want_out, want_lse = oracle.sdpa_forward(q, k, v, mask, causal=False, scale=d**-0.5)
+    name = "bfloat16" if dtype == BF16 else "float16"
+    parity(results[0][0], want_out, FWD_TOL[name], f"decode {case[0]} O")
+    parity(results[0][1], want_lse, LSE_TOL, f"decode {case[0]} L")
+    if mask_kind == "holes":
+        assert np.isnan(widen(results[0][0][-1])).all() and np.isneginf(results[0][1][-1]).all()
+    for a, b in zip(results[0], results[1], strict=True):
+        np.testing.assert_array_equal(np.ascontiguousarray(a).view(np.uint8), np.ascontiguousarray(b).view(np.uint8))
+
+
 def test_two_runs_give_the_same_bits(dev):
     import limn_standin as host
 
@@ -298,6 +354,12 @@ def test_tensor_core_path_is_the_one_that_serves_the_tuned_shapes():
     assert path(2, 256, 4096, 4096, 128, 128, 1, 0, 128**-0.5) == PATH_TCGEN05
     assert path(2, 256, 256, 256, 64, 64, 1, 0, 0.125) == PATH_TCGEN05
     assert path(1, 4, 100, 300, 64, 64, 0, 0, 0.125) == PATH_TCGEN05
+    from limn_b200._lib import PATH_DECODE
+
+    assert path(2, 64, 1, 4096, 128, 128, 0, 1, 128**-0.5) == PATH_DECODE  # a few query rows, no causal mask
+    assert path(2, 64, 4, 4096, 64, 64, 0, 0, 0.125) == PATH_DECODE
+    assert path(2, 64, 5, 4096, 64, 64, 0, 0, 0.125) == PATH_TCGEN05
+    assert path(2, 64, 1, 1, 64, 64, 1, 0, 0.125) == PATH_TCGEN05  # causal is a prefill shape, however short
     assert path(0, 2, 128, 128, 32, 32, 1, 0, 32**-0.5) == PATH_GENERAL
     assert path(2, 2, 128, 128, 64, 64, 0, 1, 0.125) == PATH_TCGEN05  # a key mask stays on the tensor-core path
     assert path(0, 2, 128, 128, 64, 64, 0, 1, 0.125) == PATH_GENERAL
