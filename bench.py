@@ -953,6 +953,29 @@ def profile_case(args) -> None:
     print(json.dumps({"profiled": args.workload, "problems": count, "backward": shard.backward, "device_status": runtime.device_status()}))
 
 
+def profile_decode(args) -> None:
+    """For profiler captures: the decode case of `others.decode` (256 problems, one query row, 4096 keys, D = 128),
+    launched `--steps` times after one warm-up launch."""
+    import torch
+
+    from limn_b200 import runtime
+    from limn_b200._lib import lib
+
+    torch.cuda.set_device(0)
+    runtime.set_device(0)
+    L = lib()
+    bh, t_k, d = 256, 4096, 128
+    q = torch.randn((bh, 1, d), device="cuda").to(torch.bfloat16)
+    k, v = (torch.randn((bh, t_k, d), device="cuda").to(torch.bfloat16) for _ in range(2))
+    out, lse = torch.empty_like(q), torch.empty((bh, 1), dtype=torch.float32, device="cuda")
+    for _ in range(1 + args.steps):
+        code = L.limn_b200_sdpa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), None, out.data_ptr(), lse.data_ptr(), 2, bh, 1, t_k, d, d, 0, d ** -0.5, None)
+        if code:
+            raise SystemExit(L.limn_b200_last_error().decode())
+    torch.cuda.synchronize()
+    print(json.dumps({"profiled": "decode one_row_4096_keys_d128", "problems": bh, "device_status": runtime.device_status()}))
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -961,6 +984,7 @@ def main() -> None:
     parser.add_argument("--impl", choices=("limn_b200", "reference"), default="limn_b200")
     parser.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT_WORKLOAD)
     parser.add_argument("--profile", type=int, default=0, metavar="N", help="launch the kernels over the first N problems and exit (for ncu)")
+    parser.add_argument("--profile-decode", action="store_true", help="launch the decode case of others.decode and exit (for ncu)")
     parser.add_argument("--backward", action="store_true", help="with --profile: run the backward kernels even for a forward-only workload")
     parser.add_argument("--no-others", dest="others", action="store_false", help="time only the named workload")
     parser.add_argument("--rest-seconds", type=float, default=0.5, help="pause before each burst trial")
@@ -970,6 +994,8 @@ def main() -> None:
     args = parser.parse_args()
     if args.limn_arm:
         limn_arm(args.limn_arm)
+    elif args.profile_decode:
+        profile_decode(args)
     elif args.profile:
         profile_case(args)
     elif args.impl == "reference":
