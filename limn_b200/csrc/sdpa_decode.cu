@@ -11,7 +11,10 @@
 // subsequence of the keys, four at a time with all eight loads (K and V) issued before the first is used, and keeps an
 // online softmax of its own per query row: a running maximum, a denominator and 8 accumulator elements per lane. The
 // groups of a warp are merged with shuffles, the 16 warps through shared memory, always in the same order, so two runs
-// give the same bits. Semantics as the oracle's (limn/sdpa.py:91-137): a hidden key contributes exactly 0, a row with
+// give the same bits. A batch too small to fill the GPU with one CTA per problem gets a thread-block cluster of up
+// to 8 CTAs per problem instead: the CTAs of a cluster deal the problem's keys out among themselves, and CTA 0 folds
+// the others' results out of their shared memory (distributed shared memory, no scratch in global memory) in rank
+// order. Semantics as the oracle's (limn/sdpa.py:91-137): a hidden key contributes exactly 0, a row with
 // no visible key is NaN with L = -inf, O is rounded once from fp32, L = m + log(l) in natural log.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -39,7 +42,25 @@ struct DecodeParams {
   Strides q_strides, k_strides;  // of q and out, of k and v, in elements
   int t_q, t_k;
   float scale;
+  int split;  // CTAs per problem (the cluster size): 1, 2, 4 or 8
 };
+
+// ---- thread-block cluster: rank, barrier, a peer CTA's shared memory ----
+__device__ __forceinline__ unsigned cluster_rank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float peer_shared(const float* mine, unsigned rank) {
+  unsigned local = static_cast<unsigned>(__cvta_generic_to_shared(mine)), remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
 
 template <bool kFp16>
 __device__ __forceinline__ void widen8(const uint4& raw, float (&f)[8]) {
@@ -75,10 +96,13 @@ __global__ void __launch_bounds__(kThreads, R <= 2 ? 2 : 1) sdpa_decode_kernel(c
   constexpr int kGroups = 32 / kLanesPerKey;    // keys per warp instruction: 2 or 4
   __shared__ float part_m[kWarps][R], part_l[kWarps][R];
   __shared__ float part_acc[kWarps][R][D];
+  __shared__ float cta_m[R], cta_l[R], cta_o[R][D];  // this CTA's share of the problem, for the cluster's CTA 0
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int group = lane / kLanesPerKey, gl = lane % kLanesPerKey;
-  const int problem = blockIdx.x;
+  const int split = prm.split;
+  const unsigned rank = split > 1 ? cluster_rank() : 0u;
+  const int problem = blockIdx.x / split;
   const int batch = problem / prm.heads, head = problem - batch * prm.heads;
   const float sl2 = prm.scale * kLog2e;
 
@@ -106,7 +130,7 @@ __global__ void __launch_bounds__(kThreads, R <= 2 ? 2 : 1) sdpa_decode_kernel(c
 
   // keys are dealt out so that the groups of a warp, and the warps of the CTA, read consecutive keys together
   constexpr int kPerPass = kWarps * kUnroll * kGroups;
-  for (int first = 0; first < prm.t_k; first += kPerPass) {
+  for (int first = rank * kPerPass; first < prm.t_k; first += split * kPerPass) {
     uint4 k_raw[kUnroll], v_raw[kUnroll];
     int key[kUnroll];
 #pragma unroll
@@ -194,7 +218,7 @@ __global__ void __launch_bounds__(kThreads, R <= 2 ? 2 : 1) sdpa_decode_kernel(c
   }
   __syncthreads();
 
-  // ---- the 16 warps: thread (r, d) folds them in warp order and writes one element ----
+  // ---- the 16 warps: thread (r, d) folds them in warp order ----
   for (int at = threadIdx.x; at < R * D; at += kThreads) {
     const int r = at / D, d = at - r * D;
     float m_tot = -INFINITY;
@@ -207,27 +231,63 @@ __global__ void __launch_bounds__(kThreads, R <= 2 ? 2 : 1) sdpa_decode_kernel(c
       l_tot = fmaf(part_l[w][r], f, l_tot);
       o = fmaf(part_acc[w][r][d], f, o);
     }
-    const float value = o / l_tot;  // 0 / 0 = NaN for a row with no visible key, as the oracle gives
-    unsigned char* dst = static_cast<unsigned char*>(prm.out) +
-                         (batch * prm.q_strides.batch + head * prm.q_strides.head + static_cast<long long>(r) * prm.q_strides.row + d) * 2;
-    if (kFp16) *reinterpret_cast<__half*>(dst) = __float2half_rn(value);
-    else *reinterpret_cast<__nv_bfloat16*>(dst) = __float2bfloat16_rn(value);
-    if (d == 0) prm.lse[static_cast<long long>(problem) * prm.t_q + r] = m_tot * prm.scale + logf(l_tot);
+    cta_o[r][d] = o;
+    if (d == 0) cta_m[r] = m_tot, cta_l[r] = l_tot;
   }
+  if (split > 1) cluster_sync();  // every CTA of the cluster has its share in shared memory
+  else __syncthreads();
+
+  // ---- the CTAs of the cluster, folded by CTA 0 in rank order; one element per thread, rounded once ----
+  if (rank == 0) {
+    for (int at = threadIdx.x; at < R * D; at += kThreads) {
+      const int r = at / D, d = at - r * D;
+      float m_tot = cta_m[r], l_tot = cta_l[r], o = cta_o[r][d];
+      for (int c = 1; c < split; ++c) {
+        const float m_c = peer_shared(&cta_m[r], c), l_c = peer_shared(&cta_l[r], c), o_c = peer_shared(&cta_o[r][d], c);
+        const float m_new = fmaxf(m_tot, m_c);
+        const float fa = m_tot == -INFINITY ? 0.f : exp2f((m_tot - m_new) * sl2);
+        const float fc = m_c == -INFINITY ? 0.f : exp2f((m_c - m_new) * sl2);
+        l_tot = l_tot * fa + l_c * fc;
+        o = o * fa + o_c * fc;
+        m_tot = m_new;
+      }
+      const float value = o / l_tot;  // 0 / 0 = NaN for a row with no visible key, as the oracle gives
+      unsigned char* dst = static_cast<unsigned char*>(prm.out) +
+                           (batch * prm.q_strides.batch + head * prm.q_strides.head + static_cast<long long>(r) * prm.q_strides.row + d) * 2;
+      if (kFp16) *reinterpret_cast<__half*>(dst) = __float2half_rn(value);
+      else *reinterpret_cast<__nv_bfloat16*>(dst) = __float2bfloat16_rn(value);
+      if (d == 0) prm.lse[static_cast<long long>(problem) * prm.t_q + r] = m_tot * prm.scale + logf(l_tot);
+    }
+  }
+  if (split > 1) cluster_sync();  // no CTA leaves while CTA 0 may still be reading its shared memory
+}
+
+template <int D, bool kFp16, bool kMask, int R>
+int launch_one(const Problem& p, const DecodeParams& prm) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(static_cast<unsigned>(p.bh * prm.split));
+  config.blockDim = dim3(kThreads);
+  config.stream = p.stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = static_cast<unsigned>(prm.split);
+  attribute[0].val.clusterDim.y = 1;
+  attribute[0].val.clusterDim.z = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  LIMN_CUDA(cudaLaunchKernelEx(&config, sdpa_decode_kernel<D, kFp16, kMask, R>, prm), "launching the sdpa decode kernel");
+  note_launches(1);
+  return LIMN_B200_OK;
 }
 
 template <int D, bool kFp16, bool kMask>
 int launch_rows(const Problem& p, const DecodeParams& prm) {
-  const dim3 grid(static_cast<unsigned>(p.bh)), block(kThreads);
   switch (p.t_q) {
-    case 1: sdpa_decode_kernel<D, kFp16, kMask, 1><<<grid, block, 0, p.stream>>>(prm); break;
-    case 2: sdpa_decode_kernel<D, kFp16, kMask, 2><<<grid, block, 0, p.stream>>>(prm); break;
-    case 3: sdpa_decode_kernel<D, kFp16, kMask, 3><<<grid, block, 0, p.stream>>>(prm); break;
-    default: sdpa_decode_kernel<D, kFp16, kMask, 4><<<grid, block, 0, p.stream>>>(prm); break;
+    case 1: return launch_one<D, kFp16, kMask, 1>(p, prm);
+    case 2: return launch_one<D, kFp16, kMask, 2>(p, prm);
+    case 3: return launch_one<D, kFp16, kMask, 3>(p, prm);
+    default: return launch_one<D, kFp16, kMask, 4>(p, prm);
   }
-  LIMN_CUDA(cudaGetLastError(), "launching the sdpa decode kernel");
-  note_launches(1);
-  return LIMN_B200_OK;
 }
 
 template <int D>
@@ -260,6 +320,14 @@ int decode_launch(const Problem& p) {
   prm.k_strides = strides_of(p.layout, prm.heads, p.t_k, p.hd);
   prm.t_q = p.t_q, prm.t_k = p.t_k;
   prm.scale = static_cast<float>(p.scale);
+  // One CTA per problem fills the GPU from a few hundred problems on (two CTAs fit an SM). Below that, 2, 4 or 8
+  // CTAs share a problem, as long as each still has a full pass of keys (16 warps x 4 in flight x keys per warp load).
+  int sms = 0;
+  if (int rc = sm_count(&sms)) return rc;
+  const int per_pass = kWarps * kUnroll * (32 / (p.hd / 8));
+  int split = 1;
+  while (split < 8 && p.bh * split * 2 <= 2LL * sms && (p.t_k + per_pass - 1) / per_pass >= split * 2) split *= 2;
+  prm.split = split;
   return p.hd == 128 ? launch_d<128>(p, prm) : launch_d<64>(p, prm);
 }
 

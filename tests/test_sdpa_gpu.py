@@ -240,6 +240,8 @@ DECODE_CASES = [
     ("bf16 d128 two rows, holes", BF16, 2, 4, 2, 777, 128, "holes", "bhtd"),
     ("bf16 d64 one row, token-major", BF16, 2, 12, 1, 640, 64, None, "bthd"),
     ("bf16 d128 one row, 3 keys", BF16, 2, 3, 1, 3, 128, None, "bhtd"),
+    ("bf16 d128 one row, 400 problems (one CTA each)", BF16, 2, 400, 1, 513, 128, None, "bhtd"),
+    ("bf16 d64 two rows, 80 problems (clusters of 2)", BF16, 2, 80, 2, 2048, 64, "pad", "bhtd"),
 ]
 
 
