@@ -147,6 +147,32 @@ int limn_b200_sdpa_bwd_kv_layout(const void* q, const void* k, const void* v, co
 int limn_b200_sdpa_delta_layout(const void* out, const void* dout, void* delta,
                                 int layout, int dtype, int batch, int heads, int t_q, int hd_v, void* stream);
 
+/* ---- operands with strides of their own ----
+ * q, k and v of an attention layer are usually slices of one projection's output, (batch, t, 3, heads, hd), and the
+ * layer's result is wanted as (batch, t, heads * hd): no single layout describes both. These entry points take one
+ * (batch, head, row) stride triple per operand, in elements (columns are contiguous; every stride a multiple of 8,
+ * every pointer 16-byte aligned and already offset to the operand's first element), so a frontend can hand over its
+ * views as they are instead of copying them (limn/tensor.py:561-562, :736-746 make those copies). lse and delta stay
+ * (batch * heads, t_q), key_mask (batch * heads, t_k). No counterpart in the reference. f16/bf16 with hd == hd_v in
+ * {64, 128} only; anything else returns LIMN_B200_UNSUPPORTED and launches nothing.
+ *   limn_b200_sdpa_fwd_strided:          strides of q, k, v, out                 (4 triples)
+ *   limn_b200_sdpa_bwd_q_fused_strided:  strides of q, k, v, out, dout, dq        (6 triples); delta is written
+ *   limn_b200_sdpa_bwd_kv_strided:       strides of q, k, v, dout, dk, dv         (6 triples) */
+int limn_b200_sdpa_fwd_strided(const void* q, const void* k, const void* v, const void* key_mask,
+                               void* out, void* lse, const long long* strides,
+                               int dtype, int batch, int heads, int t_q, int t_k, int hd, int hd_v,
+                               int causal, double scale, void* stream);
+int limn_b200_sdpa_bwd_q_fused_strided(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                                       const void* lse, const void* key_mask,
+                                       void* dq, void* delta, const long long* strides,
+                                       int dtype, int batch, int heads, int t_q, int t_k, int hd, int hd_v,
+                                       int causal, double scale, void* stream);
+int limn_b200_sdpa_bwd_kv_strided(const void* q, const void* k, const void* v, const void* dout,
+                                  const void* lse, const void* delta, const void* key_mask,
+                                  void* dk, void* dv, const long long* strides,
+                                  int dtype, int batch, int heads, int t_q, int t_k, int hd, int hd_v,
+                                  int causal, double scale, void* stream);
+
 /* Which path the dispatcher picks for a problem (a limn_b200_path value), or -1 with an
  * error message if the arguments are invalid. Launches nothing. */
 int limn_b200_sdpa_path(int dtype, long long bh, int t_q, int t_k, int hd, int hd_v,

@@ -23,6 +23,8 @@ _SHAPE = (c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_double, _P)  #
 # layout, dtype, batch, heads, t_q, t_k, hd, hd_v, causal, scale, stream
 _LAYOUT_SHAPE = (c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_double, _P)
 LAYOUT_CODES = {"bhtd": 0, "bthd": 1}
+# strides, dtype, batch, heads, t_q, t_k, hd, hd_v, causal, scale, stream
+_STRIDED_SHAPE = (POINTER(c_longlong), c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_double, _P)
 SIGNATURES = {
     "limn_b200_sdpa_fwd": (c_int, (_P, _P, _P, _P, _P, _P) + _SHAPE),
     "limn_b200_sdpa_bwd_q": (c_int, (_P, _P, _P, _P, _P, _P, _P, _P) + _SHAPE),
@@ -34,6 +36,9 @@ SIGNATURES = {
     "limn_b200_sdpa_bwd_q_layout": (c_int, (_P, _P, _P, _P, _P, _P, _P, _P) + _LAYOUT_SHAPE),
     "limn_b200_sdpa_bwd_q_fused_layout": (c_int, (_P, _P, _P, _P, _P, _P, _P, _P, _P) + _LAYOUT_SHAPE),
     "limn_b200_sdpa_bwd_kv_layout": (c_int, (_P, _P, _P, _P, _P, _P, _P, _P, _P) + _LAYOUT_SHAPE),
+    "limn_b200_sdpa_fwd_strided": (c_int, (_P, _P, _P, _P, _P, _P) + _STRIDED_SHAPE),
+    "limn_b200_sdpa_bwd_q_fused_strided": (c_int, (_P, _P, _P, _P, _P, _P, _P, _P, _P) + _STRIDED_SHAPE),
+    "limn_b200_sdpa_bwd_kv_strided": (c_int, (_P, _P, _P, _P, _P, _P, _P, _P, _P) + _STRIDED_SHAPE),
     "limn_b200_sdpa_delta_layout": (c_int, (_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P)),
     "limn_b200_sdpa_path": (c_int, (c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_double)),
     "limn_b200_last_launch_count": (c_int, ()),

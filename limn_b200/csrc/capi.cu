@@ -321,6 +321,71 @@ int limn_b200_sdpa_bwd_kv_layout(const void* q, const void* k, const void* v, co
   return dispatch_op(Op::BwdKV, "sdpa_bwd_kv", p);
 }
 
+namespace {
+
+// The strided entry points' shared argument handling: bh = batch * heads and one (batch, head, row) stride triple
+// per operand, in elements, in the order the entry point documents.
+int with_strides(const char* name, Problem& p, int batch, int heads, const long long* strides, const Operand* order, int count) {
+  if (strides == nullptr) return fail(LIMN_B200_BAD_ARGUMENT, "%s: null strides", name);
+  if (batch < 0 || heads <= 0) return fail(LIMN_B200_BAD_ARGUMENT, "%s: batch must be >= 0 and heads > 0", name);
+  p.bh = static_cast<long long>(batch) * heads;
+  p.heads = heads;
+  p.strided = true;
+  for (int i = 0; i < count; ++i) {
+    const Strides given{strides[3 * i], strides[3 * i + 1], strides[3 * i + 2]};
+    if (given.batch < 0 || given.head < 0 || given.row <= 0 || ((given.batch | given.head | given.row) & 7))
+      return fail(LIMN_B200_BAD_ARGUMENT, "%s: strides must be non-negative multiples of 8 elements (rows: positive), got (%lld, %lld, %lld) for operand %d",
+                  name, given.batch, given.head, given.row, i);
+    p.strides[order[i]] = given;
+  }
+  return LIMN_B200_OK;
+}
+
+int strided_dispatch(Op op, const char* name, const Problem& p) {
+  if (int rc = validate_op(op, name, p)) return rc;
+  if (p.bh > 0 && !tcgen05_serves(op, p))
+    return fail(LIMN_B200_UNSUPPORTED, "%s: strided operands are served for f16/bf16 with hd == hd_v in {64, 128}; make the operands contiguous for anything else", name);
+  return dispatch_op(op, name, p);
+}
+
+}  // namespace
+
+int limn_b200_sdpa_fwd_strided(const void* q, const void* k, const void* v, const void* key_mask, void* out, void* lse,
+                               const long long* strides, int dtype, int batch, int heads, int t_q, int t_k, int hd, int hd_v,
+                               int causal, double scale, void* stream) {
+  clear_error();
+  Problem p = problem(q, k, v, key_mask, dtype, 0, t_q, t_k, hd, hd_v, causal, scale, stream);
+  static const Operand order[] = {kOpQ, kOpK, kOpV, kOpOut};
+  if (int rc = with_strides("sdpa_strided", p, batch, heads, strides, order, 4)) return rc;
+  p.out = out, p.lse_out = lse;
+  return strided_dispatch(Op::Fwd, "sdpa_strided", p);
+}
+
+int limn_b200_sdpa_bwd_q_fused_strided(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                                       const void* lse, const void* key_mask, void* dq, void* delta, const long long* strides,
+                                       int dtype, int batch, int heads, int t_q, int t_k, int hd, int hd_v, int causal,
+                                       double scale, void* stream) {
+  clear_error();
+  Problem p = problem(q, k, v, key_mask, dtype, 0, t_q, t_k, hd, hd_v, causal, scale, stream);
+  static const Operand order[] = {kOpQ, kOpK, kOpV, kOpOut, kOpDout, kOpDq};
+  if (int rc = with_strides("sdpa_bwd_q_fused_strided", p, batch, heads, strides, order, 6)) return rc;
+  p.out = const_cast<void*>(out), p.dout = dout, p.lse_in = lse, p.delta = delta, p.dq = dq;
+  p.fuse_delta = true;
+  return strided_dispatch(Op::BwdQ, "sdpa_bwd_q_fused_strided", p);
+}
+
+int limn_b200_sdpa_bwd_kv_strided(const void* q, const void* k, const void* v, const void* dout, const void* lse,
+                                  const void* delta, const void* key_mask, void* dk, void* dv, const long long* strides,
+                                  int dtype, int batch, int heads, int t_q, int t_k, int hd, int hd_v, int causal, double scale,
+                                  void* stream) {
+  clear_error();
+  Problem p = problem(q, k, v, key_mask, dtype, 0, t_q, t_k, hd, hd_v, causal, scale, stream);
+  static const Operand order[] = {kOpQ, kOpK, kOpV, kOpDout, kOpDk, kOpDv};
+  if (int rc = with_strides("sdpa_bwd_kv_strided", p, batch, heads, strides, order, 6)) return rc;
+  p.dout = dout, p.lse_in = lse, p.delta = delta, p.dk = dk, p.dv = dv;
+  return strided_dispatch(Op::BwdKV, "sdpa_bwd_kv_strided", p);
+}
+
 int limn_b200_sdpa_delta_layout(const void* out, const void* dout, void* delta, int layout, int dtype, int batch,
                                 int heads, int t_q, int hd_v, void* stream) {
   clear_error();

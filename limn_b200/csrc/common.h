@@ -11,6 +11,14 @@
 
 namespace limn_b200 {
 
+// Where element (batch b, head h, row t, column 0) of an operand lives: base + b * batch + h * head + t * row
+// elements. Columns are always contiguous.
+struct Strides {
+  long long batch = 0, head = 0, row = 0;
+};
+// The operands of the three ops, for per-operand strides.
+enum Operand { kOpQ = 0, kOpK, kOpV, kOpDout, kOpOut, kOpDq, kOpDk, kOpDv, kOperands };
+
 // One attention problem, as the C ABI received it. Pointers the op does not use are null.
 struct Problem {
   const void* q = nullptr;
@@ -35,6 +43,10 @@ struct Problem {
   // With heads > 0, bh = batch * heads and problem p is (batch p / heads, head p % heads).
   int layout = 0;
   int heads = 0;
+  // The strided entry points give every operand its own strides (a q, k, v that are slices of one projection's
+  // output do not share the layout of the output they produce); otherwise the strides follow from `layout`.
+  bool strided = false;
+  Strides strides[kOperands];
   // dQ pass only: compute delta from `out` (the forward's O) and dO on the way and write it to `delta`, instead of
   // reading it. Served by the tensor-core kernels; the general family runs the row-dot kernel first.
   bool fuse_delta = false;
@@ -78,6 +90,13 @@ int sm_count(int* count);
 // (extents, dtype, required pointers, layout support) and launches nothing; dispatch_op checks, then launches.
 int validate_op(Op op, const char* name, const Problem& p);
 int dispatch_op(Op op, const char* name, const Problem& p);
+
+// Strides of a (batch, heads, rows, width) operand in the given limn_b200_layout, and of operand `which` of a
+// problem: the ones the caller gave, else the layout's.
+Strides strides_of(int layout, int heads, int rows, int width);
+inline Strides operand_strides(const Problem& p, Operand which, int heads, int rows, int width) {
+  return p.strided ? p.strides[which] : strides_of(p.layout, heads, rows, width);
+}
 
 // Launch with programmatic stream serialization: the kernel may be scheduled while the last CTAs of the kernel
 // before it in the stream are still running, and waits for that kernel itself (ptx::grid_dependency_wait) before

@@ -132,7 +132,9 @@ struct BwdParams {
   unsigned* schedule;  // [0] next work item, [1] CTAs that have finished; both zero between launches
   int group;           // problems per scheduling group (see cta_work)
   int heads;           // problem p is (batch p / heads, head p % heads) in the tensor maps and in the outputs
-  Strides out_strides; // of dQ (dQ pass) or of dK and dV (dK/dV pass), in elements
+  Strides out_strides; // of dQ (dQ pass) or of dK (dK/dV pass), in elements
+  Strides out1_strides;  // of dV
+  Strides o_strides, do_strides;  // fused dQ pass: of the rows of O and dO the row statistic is computed from
   unsigned items;      // work items: bh * (tiles of 128 rows a problem's owner side has)
   int t_q, t_k;
   int q_tiles, kv_tiles;
@@ -792,7 +794,8 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       if (kKV) {
         // group 0 writes this key's dV row, group 1 its dK row
         const bool in = row < prm.t_k;
-        const long long out_at = item.batch * prm.out_strides.batch + item.head * prm.out_strides.head + row * prm.out_strides.row;
+        const Strides& mine = group == 0 ? prm.out1_strides : prm.out_strides;
+        const long long out_at = item.batch * mine.batch + item.head * mine.head + row * mine.row;
         const uint32_t t_acc = tmem + lane_base + (group == 0 ? L::kAcc0 : L::kAcc1);
         void* dst = group == 0 ? prm.out1 : prm.out0;
         const float mul = group == 0 ? 1.f : prm.scale;
@@ -846,8 +849,9 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       for (int half = 0; half < 2; ++half) {
         const int local = j + 64 * half;
         const int row = min(item.own0 + local, prm.t_q - 1);
-        const long long at = (item.batch * prm.out_strides.batch + item.head * prm.out_strides.head + row * prm.out_strides.row) * 2;
-        const float d = row_dot<D, kFp16>(static_cast<const unsigned char*>(prm.o_rows) + at, static_cast<const unsigned char*>(prm.do_rows) + at);
+        const long long o_at = (item.batch * prm.o_strides.batch + item.head * prm.o_strides.head + row * prm.o_strides.row) * 2;
+        const long long do_at = (item.batch * prm.do_strides.batch + item.head * prm.do_strides.head + row * prm.do_strides.row) * 2;
+        const float d = row_dot<D, kFp16>(static_cast<const unsigned char*>(prm.o_rows) + o_at, static_cast<const unsigned char*>(prm.do_rows) + do_at);
         delta_ring[slot][local] = d;
         if (item.own0 + local < prm.t_q) prm.delta_out[static_cast<long long>(item.problem) * prm.t_q + row] = d;
       }
@@ -880,11 +884,10 @@ int launch_bwd(const Problem& p) {
   using L = BwdLayout<D, kKV, kMask>;
   CUtensorMap map_q, map_k, map_v, map_do;
   const int heads = p.heads > 0 ? p.heads : static_cast<int>(p.bh), batch = static_cast<int>(p.bh / heads);
-  const Strides of_q = strides_of(p.layout, heads, p.t_q, D), of_k = strides_of(p.layout, heads, p.t_k, D);
-  if (int rc = make_tile_map(&map_q, p.q, kFp16, batch, heads, p.t_q, D, kTile, of_q)) return rc;
-  if (int rc = make_tile_map(&map_k, p.k, kFp16, batch, heads, p.t_k, D, kTile, of_k)) return rc;
-  if (int rc = make_tile_map(&map_v, p.v, kFp16, batch, heads, p.t_k, D, kTile, of_k)) return rc;
-  if (int rc = make_tile_map(&map_do, p.dout, kFp16, batch, heads, p.t_q, D, kTile, of_q)) return rc;
+  if (int rc = make_tile_map(&map_q, p.q, kFp16, batch, heads, p.t_q, D, kTile, operand_strides(p, kOpQ, heads, p.t_q, D))) return rc;
+  if (int rc = make_tile_map(&map_k, p.k, kFp16, batch, heads, p.t_k, D, kTile, operand_strides(p, kOpK, heads, p.t_k, D))) return rc;
+  if (int rc = make_tile_map(&map_v, p.v, kFp16, batch, heads, p.t_k, D, kTile, operand_strides(p, kOpV, heads, p.t_k, D))) return rc;
+  if (int rc = make_tile_map(&map_do, p.dout, kFp16, batch, heads, p.t_q, D, kTile, operand_strides(p, kOpDout, heads, p.t_q, D))) return rc;
   BwdParams prm;
   prm.mask = static_cast<const unsigned short*>(p.mask);
   prm.lse = static_cast<const float*>(p.lse_in);
@@ -895,7 +898,17 @@ int launch_bwd(const Problem& p) {
   prm.out0 = kKV ? p.dk : p.dq;
   prm.out1 = kKV ? p.dv : nullptr;
   prm.heads = heads;
-  prm.out_strides = kKV ? of_k : of_q;
+  prm.out_strides = kKV ? operand_strides(p, kOpDk, heads, p.t_k, D) : operand_strides(p, kOpDq, heads, p.t_q, D);
+  prm.out1_strides = operand_strides(p, kOpDv, heads, p.t_k, D);
+  prm.o_strides = operand_strides(p, kOpOut, heads, p.t_q, D);
+  prm.do_strides = operand_strides(p, kOpDout, heads, p.t_q, D);
+  {
+    const long long all = prm.out_strides.batch | prm.out_strides.head | prm.out_strides.row | prm.out1_strides.batch |
+                          prm.out1_strides.head | prm.out1_strides.row | prm.o_strides.batch | prm.o_strides.head | prm.o_strides.row;
+    if (all & 7) return fail(LIMN_B200_BAD_ARGUMENT, "sdpa backward: operand strides must be multiples of 8 elements");
+    const uintptr_t bases = reinterpret_cast<uintptr_t>(prm.out0) | reinterpret_cast<uintptr_t>(prm.out1) | reinterpret_cast<uintptr_t>(prm.o_rows);
+    if (bases & 15u) return fail(LIMN_B200_BAD_ARGUMENT, "sdpa backward: an output (or O) is not 16-byte aligned");
+  }
   prm.status = p.status;
   if (prm.status == nullptr)
     if (int rc = status_word(&prm.status)) return rc;

@@ -39,7 +39,7 @@ struct DecodeParams {
   void* out;
   float* lse;
   int heads;  // problem p is (batch p / heads, head p % heads)
-  Strides q_strides, k_strides;  // of q and out, of k and v, in elements
+  Strides q_strides, k_strides, v_strides, o_strides;  // in elements
   int t_q, t_k;
   float scale;
   int split;  // CTAs per problem (the cluster size): 1, 2, 4 or 8
@@ -108,8 +108,8 @@ __global__ void __launch_bounds__(kThreads, R <= 2 ? 2 : 1) sdpa_decode_kernel(c
 
   const unsigned char* q_base = static_cast<const unsigned char*>(prm.q) + (batch * prm.q_strides.batch + head * prm.q_strides.head) * 2;
   const unsigned char* k_base = static_cast<const unsigned char*>(prm.k) + (batch * prm.k_strides.batch + head * prm.k_strides.head) * 2;
-  const unsigned char* v_base = static_cast<const unsigned char*>(prm.v) + (batch * prm.k_strides.batch + head * prm.k_strides.head) * 2;
-  const long long k_row = prm.k_strides.row * 2;  // bytes between keys
+  const unsigned char* v_base = static_cast<const unsigned char*>(prm.v) + (batch * prm.v_strides.batch + head * prm.v_strides.head) * 2;
+  const long long k_row = prm.k_strides.row * 2, v_row = prm.v_strides.row * 2;  // bytes between keys
   const unsigned short* flags = kMask ? prm.mask + static_cast<long long>(problem) * prm.t_k : nullptr;
 
   // this lane's 8 elements of every query row
@@ -142,7 +142,7 @@ __global__ void __launch_bounds__(kThreads, R <= 2 ? 2 : 1) sdpa_decode_kernel(c
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int at = min(key[u], prm.t_k - 1);
-      v_raw[u] = *reinterpret_cast<const uint4*>(v_base + at * k_row + gl * 16);
+      v_raw[u] = *reinterpret_cast<const uint4*>(v_base + at * v_row + gl * 16);
     }
     float s[R][kUnroll];
 #pragma unroll
@@ -253,7 +253,7 @@ __global__ void __launch_bounds__(kThreads, R <= 2 ? 2 : 1) sdpa_decode_kernel(c
       }
       const float value = o / l_tot;  // 0 / 0 = NaN for a row with no visible key, as the oracle gives
       unsigned char* dst = static_cast<unsigned char*>(prm.out) +
-                           (batch * prm.q_strides.batch + head * prm.q_strides.head + static_cast<long long>(r) * prm.q_strides.row + d) * 2;
+                           (batch * prm.o_strides.batch + head * prm.o_strides.head + static_cast<long long>(r) * prm.o_strides.row + d) * 2;
       if (kFp16) *reinterpret_cast<__half*>(dst) = __float2half_rn(value);
       else *reinterpret_cast<__nv_bfloat16*>(dst) = __float2bfloat16_rn(value);
       if (d == 0) prm.lse[static_cast<long long>(problem) * prm.t_q + r] = m_tot * prm.scale + logf(l_tot);
@@ -316,8 +316,15 @@ int decode_launch(const Problem& p) {
   prm.mask = static_cast<const unsigned short*>(p.mask);
   prm.out = p.out, prm.lse = static_cast<float*>(p.lse_out);
   prm.heads = p.heads > 0 ? p.heads : static_cast<int>(p.bh);
-  prm.q_strides = strides_of(p.layout, prm.heads, p.t_q, p.hd);
-  prm.k_strides = strides_of(p.layout, prm.heads, p.t_k, p.hd);
+  prm.q_strides = operand_strides(p, kOpQ, prm.heads, p.t_q, p.hd);
+  prm.k_strides = operand_strides(p, kOpK, prm.heads, p.t_k, p.hd);
+  prm.v_strides = operand_strides(p, kOpV, prm.heads, p.t_k, p.hd);
+  prm.o_strides = operand_strides(p, kOpOut, prm.heads, p.t_q, p.hd);
+  {
+    const long long all = prm.q_strides.batch | prm.q_strides.head | prm.q_strides.row | prm.k_strides.batch | prm.k_strides.head |
+                          prm.k_strides.row | prm.v_strides.batch | prm.v_strides.head | prm.v_strides.row;
+    if (all & 7) return fail(LIMN_B200_BAD_ARGUMENT, "sdpa: operand strides must be multiples of 8 elements");
+  }
   prm.t_q = p.t_q, prm.t_k = p.t_k;
   prm.scale = static_cast<float>(p.scale);
   // One CTA per problem fills the GPU from a few hundred problems on (two CTAs fit an SM). Below that, 2, 4 or 8

@@ -584,14 +584,16 @@ int launch_fwd(const Problem& p) {
   using L = FwdLayout<D>;
   CUtensorMap map_q, map_k, map_v;
   const int heads = p.heads > 0 ? p.heads : static_cast<int>(p.bh), batch = static_cast<int>(p.bh / heads);
-  const Strides of_q = strides_of(p.layout, heads, p.t_q, D), of_k = strides_of(p.layout, heads, p.t_k, D);
-  if (int rc = make_tile_map(&map_q, p.q, kFp16, batch, heads, p.t_q, D, kTileRows, of_q)) return rc;
-  if (int rc = make_tile_map(&map_k, p.k, kFp16, batch, heads, p.t_k, D, kTileRows, of_k)) return rc;
-  if (int rc = make_tile_map(&map_v, p.v, kFp16, batch, heads, p.t_k, D, kTileRows, of_k)) return rc;
+  if (int rc = make_tile_map(&map_q, p.q, kFp16, batch, heads, p.t_q, D, kTileRows, operand_strides(p, kOpQ, heads, p.t_q, D))) return rc;
+  if (int rc = make_tile_map(&map_k, p.k, kFp16, batch, heads, p.t_k, D, kTileRows, operand_strides(p, kOpK, heads, p.t_k, D))) return rc;
+  if (int rc = make_tile_map(&map_v, p.v, kFp16, batch, heads, p.t_k, D, kTileRows, operand_strides(p, kOpV, heads, p.t_k, D))) return rc;
   FwdParams prm;
   prm.out = p.out;
   prm.heads = heads;
-  prm.out_strides = of_q;
+  prm.out_strides = operand_strides(p, kOpOut, heads, p.t_q, D);
+  if ((prm.out_strides.batch | prm.out_strides.head | prm.out_strides.row) & 7)
+    return fail(LIMN_B200_BAD_ARGUMENT, "sdpa: operand strides must be multiples of 8 elements");
+  if (reinterpret_cast<uintptr_t>(p.out) & 15u) return fail(LIMN_B200_BAD_ARGUMENT, "sdpa: the output is not 16-byte aligned");
   prm.mask = static_cast<const unsigned short*>(p.mask);
   prm.lse = static_cast<float*>(p.lse_out);
   prm.status = p.status;

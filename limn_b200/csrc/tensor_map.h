@@ -4,15 +4,9 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
-namespace limn_b200 {
+#include "common.h"
 
-// Where element (batch b, head h, row t, column 0) of an operand lives: base + b * batch + h * head + t * row
-// elements. Columns are always contiguous.
-struct Strides {
-  long long batch, head, row;
-};
-// Strides of a (batch, heads, rows, width) operand in the given limn_b200_layout.
-Strides strides_of(int layout, int heads, int rows, int width);
+namespace limn_b200 {
 
 // A 4-D map (column, row, head, batch) over an operand of 2-byte elements, fetched in boxes of `box_rows`
 // rows by 64 elements (128 bytes) of one (batch, head) problem, written to shared memory with the 128-byte

@@ -100,6 +100,58 @@ def test_token_major_with_a_key_mask_matches_the_oracle():
     assert (widen(got["dk"].transpose(0, 2, 1, 3))[:, :, 150:] == 0).all()
 
 
+@pytest.mark.parametrize("hd,causal,t", [(64, True, 300), (128, False, 257)], ids=["d64 causal", "d128 full"])
+def test_slices_of_one_projection_buffer_give_the_dense_bits(hd, causal, t):
+    """The strided entry points on what a transformer layer really holds: q, k, v as slices of one
+    (batch, t, 3, heads, hd) projection output, dO and the results token-major, dK and dV written straight into a
+    (batch, t, 2, heads, hd) buffer. Bit for bit what the dense entry points give on dense copies."""
+    import ctypes
+
+    from limn_b200 import runtime
+    from limn_b200._lib import check, lib
+
+    L = lib()
+    batch, heads = 2, 3
+    dense = _inputs(35, batch, heads, t, t, hd, BF16)
+    want = _run("bhtd", dense, None, batch, heads, t, t, hd, causal, BF16)
+    qkv = np.stack([a.transpose(0, 2, 1, 3) for a in dense[:3]], axis=2)  # (batch, t, 3, heads, hd)
+    do = np.ascontiguousarray(dense[3].transpose(0, 2, 1, 3))               # (batch, t, heads, hd)
+    qkv_dev, do_dev = runtime.upload(np.ascontiguousarray(qkv)), runtime.upload(do)
+    row3, row2, row1 = 3 * heads * hd, 2 * heads * hd, heads * hd
+    in_qkv = (t * row3, hd, row3)       # (batch, head, row) strides of a slice of the projection buffer
+    token_major = (t * row1, hd, row1)
+    in_kv_grad = (t * row2, hd, row2)
+    q_ptr, k_ptr, v_ptr = (qkv_dev.ptr + i * row1 * 2 for i in range(3))
+    out, dq = runtime.empty(do.nbytes), runtime.empty(do.nbytes)
+    dkv = runtime.empty(2 * do.nbytes)
+    lse, delta = runtime.empty(batch * heads * t * 4), runtime.empty(batch * heads * t * 4)
+    arr = lambda *triples: (ctypes.c_longlong * (3 * len(triples)))(*[x for tr in triples for x in tr])
+    tail = (2, batch, heads, t, t, hd, hd, int(causal), hd**-0.5, None)
+    check(L.limn_b200_sdpa_fwd_strided(q_ptr, k_ptr, v_ptr, None, out.ptr, lse.ptr, arr(in_qkv, in_qkv, in_qkv, token_major), *tail), "sdpa")
+    check(L.limn_b200_sdpa_bwd_q_fused_strided(q_ptr, k_ptr, v_ptr, out.ptr, do_dev.ptr, lse.ptr, None, dq.ptr, delta.ptr,
+                                               arr(in_qkv, in_qkv, in_qkv, token_major, token_major, token_major), *tail), "dq")
+    check(L.limn_b200_sdpa_bwd_kv_strided(q_ptr, k_ptr, v_ptr, do_dev.ptr, lse.ptr, delta.ptr, None, dkv.ptr, dkv.ptr + row1 * 2,
+                                          arr(in_qkv, in_qkv, in_qkv, token_major, in_kv_grad, in_kv_grad), *tail), "dk, dv")
+    runtime.synchronize()
+    assert runtime.device_status() == 0
+    got_out = runtime.download(out, BF16, (batch, t, heads, hd)).transpose(0, 2, 1, 3)
+    got_dq = runtime.download(dq, BF16, (batch, t, heads, hd)).transpose(0, 2, 1, 3)
+    got_dkv = runtime.download(dkv, BF16, (batch, t, 2, heads, hd))
+    np.testing.assert_array_equal(got_out.view(np.uint16), want["out"].view(np.uint16))
+    np.testing.assert_array_equal(runtime.download(lse, np.uint32, (batch, heads, t)), want["lse"].view(np.uint32))
+    # the fused row dot sums in another order than the reduce kernel: gradients agree to a bfloat16 step
+    for got, name in ((got_dq, "dq"), (got_dkv[:, :, 0].transpose(0, 2, 1, 3), "dk"), (got_dkv[:, :, 1].transpose(0, 2, 1, 3), "dv")):
+        np.testing.assert_allclose(widen(got), widen(want[name]), rtol=2**-7, atol=2e-3, err_msg=name)
+    # misuse is refused before anything is launched
+    from limn_b200._lib import last_error
+
+    bad = arr((t * row3, hd, row3 + 4), in_qkv, in_qkv, token_major)
+    assert L.limn_b200_sdpa_fwd_strided(q_ptr, k_ptr, v_ptr, None, out.ptr, lse.ptr, bad, *tail) == 1 and "multiples of 8" in last_error()
+    assert L.limn_b200_sdpa_fwd_strided(q_ptr, k_ptr, v_ptr, None, out.ptr, lse.ptr, None, *tail) == 1
+    assert L.limn_b200_sdpa_fwd_strided(q_ptr, k_ptr, v_ptr, None, out.ptr, lse.ptr, arr(in_qkv, in_qkv, in_qkv, token_major),
+                                        0, batch, heads, t, t, hd, hd, int(causal), hd**-0.5, None) == 2  # float32: not served strided
+
+
 def test_dense_layout_code_is_the_dense_entry_point():
     from limn_b200 import runtime
     from limn_b200._lib import check, lib
