@@ -778,11 +778,14 @@ def gpu_arm(args) -> None:
 # ---------------------------------------------------------------- limn itself on the GPU
 
 
-def gpt_step(limn, *, dim: int, heads: int, layers: int, ctx: int, vocab: int = 256, attention_dtype=None):
+def gpt_step(limn, *, dim: int, heads: int, layers: int, ctx: int, vocab: int = 256, attention_dtype=None, cast_in_place: bool = False):
     """A byte-level GPT training step shaped like limn's examples/train_stories.py (pre-norm blocks of causal
     attention and a 4x MLP, learned positions, AdamW, the loss realised with the update), at a width of our
     choosing and with the attention operands optionally cast to a half-width dtype, which is what puts the
-    layer on the tensor-core kernels. Returns (step(tokens, targets) -> loss, parameters)."""
+    layer on the tensor-core kernels. `cast_in_place` moves the two casts to where the data lies token-major (the
+    projection's output before it is sliced into q, k, v; the attention's result after it is reshaped back), which is
+    what lets limn_b200.frontend.read_views_in_place() hand the kernels the views themselves. Returns
+    (step(tokens, targets) -> loss, parameters)."""
     from limn.nn import Embedding, LayerNorm, Linear, parameters
     from limn.optim import AdamW
 
@@ -796,13 +799,19 @@ def gpt_step(limn, *, dim: int, heads: int, layers: int, ctx: int, vocab: int = 
 
         def __call__(self, x):
             b, t, c = x.shape
-            q, k, v = self.to_qkv(self.norm_attention(x)).reshape(b, t, 3, heads, c // heads).permute(2, 0, 3, 1, 4)
-            if attention_dtype is not None:
+            projected = self.to_qkv(self.norm_attention(x))
+            if attention_dtype is not None and cast_in_place:
+                projected = projected.cast(attention_dtype)
+            q, k, v = projected.reshape(b, t, 3, heads, c // heads).permute(2, 0, 3, 1, 4)
+            if attention_dtype is not None and not cast_in_place:
                 q, k, v = q.cast(attention_dtype), k.cast(attention_dtype), v.cast(attention_dtype)
             mixed = q.attention(k, v, causal=True)
-            if attention_dtype is not None:
+            if attention_dtype is not None and not cast_in_place:
                 mixed = mixed.cast(limn.float32)
-            x = x + self.to_out(mixed.permute(0, 2, 1, 3).reshape(b, t, c))
+            mixed = mixed.permute(0, 2, 1, 3).reshape(b, t, c)
+            if attention_dtype is not None and cast_in_place:
+                mixed = mixed.cast(limn.float32)
+            x = x + self.to_out(mixed)
             return x + self.narrow(self.widen(self.norm_mlp(x)).relu())
 
     class Model:
@@ -888,32 +897,40 @@ def limn_arm(workload: str) -> None:
             entry["fwd_bwd_ms"], entry["fwd_bwd_tflops"] = ms, 3.5 * fwd_flops(problems, s, d, causal) / (ms * 1e-3) / 1e12
         return entry
 
-    def gpt_case(reps: int) -> dict:
+    def gpt_case(reps: int, cast_in_place: bool = False) -> dict:
         ctx, batch = 256, 32
         limn.set_seed(0)
-        step, params = gpt_step(limn, dim=512, heads=8, layers=6, ctx=ctx, attention_dtype=limn.bfloat16)
+        step, params = gpt_step(limn, dim=512, heads=8, layers=6, ctx=ctx, attention_dtype=limn.bfloat16, cast_in_place=cast_in_place)
         tokens = rng.integers(0, 256, size=(batch, ctx + 1)).astype(np.int32)
         args = (limn.Tensor(tokens[:, :-1]), limn.Tensor(tokens[:, 1:]))
         ms = replay_ms(step, args, reps)
         return {"ms_per_step": ms, "tokens_per_s": batch * ctx / (ms * 1e-3), "model": "6 layers, d_model 512, 8 heads x 64, context 256, batch 32, "
                 "float32 model with bfloat16 attention operands, synthetic byte tokens, AdamW step included", "parameters": int(sum(p.numel for p in params))}
 
+    from limn_b200 import frontend as patches
+
     found = {"timing": "wall clock around replays of a captured step, each ending in the device's finish(); best of 3 trials",
-             "kernels_as_shipped": {}, "limn_b200_installed": {}}
-    for label, install in (("kernels_as_shipped", False), ("limn_b200_installed", True)):
+             "kernels_as_shipped": {}, "limn_b200_installed": {},
+             "limn_b200_installed_and_frontend_patched": {"patches": "limn_b200.frontend.fuse_row_dot() and read_views_in_place(); the model casts where the "
+                                                                     "data lies token-major (gpt_step cast_in_place)"}}
+    for label, install in (("kernels_as_shipped", False), ("limn_b200_installed", True), ("limn_b200_installed_and_frontend_patched", True)):
         limn.device.set_device("cuda")
         if install:
             limn_b200.install(limn.device.active())
+        patched = label.endswith("patched")
+        undo = [patches.fuse_row_dot(), patches.read_views_in_place()] if patched else []
         try:
             # the main workload on a subset of its problems (limn's scalar kernels need seconds for all of them), the GPT
             # attention layer in full, and the whole 6-layer training step around it
             found[label][workload] = attention_case(workload, 16, 3)
             if workload != "gpt_layer":
                 found[label]["gpt_layer"] = attention_case("gpt_layer", 256, 10)
-            found[label]["gpt_train_step"] = gpt_case(5)
+            found[label]["gpt_train_step"] = gpt_case(5, cast_in_place=patched)
         except Exception as err:
             found[label]["error"] = f"{type(err).__name__}: {err}"[:300]
         finally:
+            for restore in undo:
+                restore()
             limn.device.set_device("numpy")
     print(json.dumps(found), flush=True)
 

@@ -144,12 +144,111 @@ def build_sdpa_bwd_q_fused(node: Any) -> Runner:
     return run
 
 
+class StridedForm:
+    """A "*_strided" CUSTOM node (built by limn_b200.frontend.read_views_in_place): srcs are the buffers under the
+    operands' views, params carry (causal, scale, (batch, heads, t_q, t_k, hd), per-view (offset, batch, head, row
+    strides) in elements). Several operands may sit on one buffer (q, k and v of one projection): the plan then
+    hands that buffer over once (limn/schedule.py: fuse() lists a kernel's inputs without repeats), in the order
+    of first appearance among the srcs, which `slot` reproduces."""
+
+    def __init__(self, node: Any, outputs: int):
+        self.name = node.arg.name
+        causal, scale, (batch, heads, t_q, t_k, hd), self.views = node.arg.params
+        self.causal, self.scale = bool(causal), float(scale)
+        self.batch, self.heads, self.t_q, self.t_k, self.hd = batch, heads, t_q, t_k, hd
+        dtype = node.srcs[0].dtype
+        if dtype.name not in ("float16", "bfloat16"):
+            raise NotImplementedError(f"limn_b200: {self.name} has no kernel for dtype {dtype.name}")
+        self.dtype = DTYPE_CODES[dtype.name]
+        unique = list(dict.fromkeys(node.srcs))
+        self.slot = [unique.index(src) for src in node.srcs]
+        self.inputs = len(unique)
+        if len(node.arg.outs) != outputs:
+            raise ValueError(f"limn_b200: {self.name} writes {outputs} outputs, the node declares {len(node.arg.outs)}")
+        self.outputs = outputs
+
+    def token_major(self, t: int) -> tuple[int, int, int]:
+        """(batch, head, row) strides of a dense (batch, t, heads, hd) result."""
+        return (t * self.heads * self.hd, self.hd, self.heads * self.hd)
+
+    def strides(self, *triples: tuple[int, int, int]):
+        flat = [x for triple in triples for x in triple]
+        return (ctypes.c_longlong * len(flat))(*flat)
+
+    def tail(self) -> tuple:
+        return (self.dtype, self.batch, self.heads, self.t_q, self.t_k, self.hd, self.hd, int(self.causal), self.scale, None)
+
+    def pointers(self, inputs: list[Any], outs: list[Any]) -> tuple[list[int], list[int]]:
+        if len(inputs) != self.inputs or len(outs) != self.outputs:
+            raise RuntimeError(
+                f"limn_b200: {self.name} was built for {self.inputs} buffers and {self.outputs} outputs, "
+                f"called with {len(inputs)} and {len(outs)}"
+            )
+        return [inputs[s].ptr for s in self.slot], [buf.ptr for buf in outs]
+
+
+def build_sdpa_strided(node: Any) -> Runner:
+    """Runner for "sdpa_strided": buffers under (q, k, v) -> outs (O token-major, L)."""
+    form = StridedForm(node, 2)
+    fn = lib().limn_b200_sdpa_fwd_strided
+    strides = form.strides(*[view[1:] for view in form.views[:3]], form.token_major(form.t_q))
+    offsets = [view[0] * 2 for view in form.views[:3]]
+    tail = form.tail()
+
+    def run(inputs: list[Any], outs: list[Any]) -> None:
+        ins, (out, lse) = form.pointers(inputs, outs)
+        q, k, v = (ins[i] + offsets[i] for i in range(3))
+        check(fn(q, k, v, None, out, lse, strides, *tail), "launching sdpa_strided")
+        _note_launch()
+
+    return run
+
+
+def build_sdpa_bwd_q_fused_strided(node: Any) -> Runner:
+    """Runner for "sdpa_bwd_q_fused_strided": buffers under (q, k, v), O, buffer under dO, L -> outs (dQ token-major, delta)."""
+    form = StridedForm(node, 2)
+    fn = lib().limn_b200_sdpa_bwd_q_fused_strided
+    major = form.token_major(form.t_q)
+    strides = form.strides(*[view[1:] for view in form.views[:3]], major, form.views[3][1:], major)
+    offsets = [view[0] * 2 for view in form.views]
+    tail = form.tail()
+
+    def run(inputs: list[Any], outs: list[Any]) -> None:
+        ins, (dq, delta) = form.pointers(inputs, outs)
+        q, k, v = (ins[i] + offsets[i] for i in range(3))
+        check(fn(q, k, v, ins[3], ins[4] + offsets[3], ins[5], None, dq, delta, strides, *tail), "launching sdpa_bwd_q_fused_strided")
+        _note_launch()
+
+    return run
+
+
+def build_sdpa_bwd_kv_strided(node: Any) -> Runner:
+    """Runner for "sdpa_bwd_kv_strided": buffers under (q, k, v), buffer under dO, L, delta -> outs (dK, dV token-major)."""
+    form = StridedForm(node, 2)
+    fn = lib().limn_b200_sdpa_bwd_kv_strided
+    major = form.token_major(form.t_k)
+    strides = form.strides(*[view[1:] for view in form.views[:3]], form.views[3][1:], major, major)
+    offsets = [view[0] * 2 for view in form.views]
+    tail = form.tail()
+
+    def run(inputs: list[Any], outs: list[Any]) -> None:
+        ins, (dk, dv) = form.pointers(inputs, outs)
+        q, k, v = (ins[i] + offsets[i] for i in range(3))
+        check(fn(q, k, v, ins[3] + offsets[3], ins[4], ins[5], None, dk, dv, strides, *tail), "launching sdpa_bwd_kv_strided")
+        _note_launch()
+
+    return run
+
+
 SDPA_BWD_Q_FUSED = "sdpa_bwd_q_fused"
 BUILDERS: dict[str, Callable[[Any], Runner]] = {
     SDPA: build_sdpa,
     SDPA_BWD_Q: build_sdpa_bwd_q,
     SDPA_BWD_KV: build_sdpa_bwd_kv,
     SDPA_BWD_Q_FUSED: build_sdpa_bwd_q_fused,
+    "sdpa_strided": build_sdpa_strided,
+    "sdpa_bwd_q_fused_strided": build_sdpa_bwd_q_fused_strided,
+    "sdpa_bwd_kv_strided": build_sdpa_bwd_kv_strided,
 }
 
 
@@ -187,8 +286,9 @@ def check_device_status(doing: str = "waiting for the batch") -> None:
 
 def install(device: Any) -> Any:
     """Register the builders on a device that has a `custom` registry (limn's CompiledDevice,
-    limn/jit.py:103-135): limn's three names, and "sdpa_bwd_q_fused", which limn's frontend only asks
-    for after limn_b200.frontend.fuse_row_dot(). Loads the shared library first, so a missing or
+    limn/jit.py:103-135): limn's three names, and the names limn's frontend only asks for once it has been
+    patched: "sdpa_bwd_q_fused" (limn_b200.frontend.fuse_row_dot) and the three "*_strided" ones
+    (limn_b200.frontend.read_views_in_place). Loads the shared library first, so a missing or
     unloadable library fails here rather than at the first step.
 
     The device's finish() (limn's one synchronise per batch, limn/jit.py:183) is wrapped so that

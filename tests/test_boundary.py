@@ -160,7 +160,8 @@ def test_install_needs_a_registry():
             self.custom = {}
 
     dev = limn_b200.install(WithRegistry())
-    assert set(dev.custom) == {"sdpa", "sdpa_bwd_q", "sdpa_bwd_kv", "sdpa_bwd_q_fused"}
+    assert set(dev.custom) == {"sdpa", "sdpa_bwd_q", "sdpa_bwd_kv", "sdpa_bwd_q_fused", "sdpa_strided", "sdpa_bwd_q_fused_strided",
+                               "sdpa_bwd_kv_strided"}
 
 
 def test_installed_finish_reports_a_kernel_that_gave_up(monkeypatch):
@@ -313,5 +314,61 @@ def test_the_frontend_patch_swaps_the_row_dot_for_the_fused_op():
         finally:
             undo()
         assert frontend._attention_backward is before
+    finally:
+        sys.path.remove(str(REFERENCE))
+
+
+@pytest.mark.skipif(not (REFERENCE / "limn").is_dir(), reason="the reference checkout is not on this machine")
+def test_the_frontend_patch_hands_views_over_in_place():
+    """limn_b200.frontend.read_views_in_place(): q, k, v taken as slices of one projection reach the CUSTOM nodes
+    as the buffer under them plus strides (no CONTIGUOUS copy per operand), the result comes back token-major, and
+    calls that do not qualify (float32 here) go to limn's own Tensor.attention. Graph level only."""
+    sys.path.insert(0, str(REFERENCE))
+    try:
+        import limn
+        import limn.device as device_module
+        from limn import backend_c
+        from limn.ops import Op, topological
+
+        import limn_b200
+        from limn_b200 import frontend as patch
+
+        undo = patch.read_views_in_place()
+        dev = limn_b200.install(backend_c.CDevice())
+        original = device_module.DEVICES["c"]
+        device_module.DEVICES["c"] = lambda: dev
+        try:
+            limn.set_device("c")
+            b, t, heads, hd = 2, 16, 2, 64
+            rng = np.random.default_rng(0)
+
+            def layer_gradient(dtype):
+                x = limn.Tensor(rng.standard_normal((b, t, 3 * heads * hd)).astype(np.float32), requires_grad=True)
+                q, k, v = x.cast(dtype).reshape(b, t, 3, heads, hd).permute(2, 0, 3, 1, 4)
+                y = q.attention(k, v, causal=True).permute(0, 2, 1, 3).reshape(b, t, heads * hd).cast(limn.float32)
+                (g,) = limn.grad((y * y).sum(), [x])
+                return topological([g.node])
+
+            nodes = layer_gradient(limn.bfloat16)
+            customs = [n for n in nodes if n.op is Op.CUSTOM and n.arg.index == 0]
+            assert sorted(n.arg.name for n in customs) == ["sdpa_bwd_kv_strided", "sdpa_bwd_q_fused_strided", "sdpa_strided"]
+            forward = next(n for n in customs if n.arg.name == "sdpa_strided")
+            causal, scale, extents, views = forward.arg.params
+            row = 3 * heads * hd
+            assert extents == (b, heads, t, t, hd) and causal is True
+            assert views == ((0, t * row, hd, row), (heads * hd, t * row, hd, row), (2 * heads * hd, t * row, hd, row))
+            assert forward.srcs[0] is forward.srcs[1] is forward.srcs[2], "q, k and v sit on one buffer"
+            assert forward.arg.outs[0][1] == (b, t, heads, hd), "the result is token-major"
+            # one buffer for the projection, one for the gradient that comes back: no copy per operand
+            assert sum(1 for n in nodes if n.op is Op.CONTIGUOUS) <= 3
+            dq = next(n for n in customs if n.arg.name == "sdpa_bwd_q_fused_strided")
+            assert dq.arg.params[3][3] == (0, t * heads * hd, hd, heads * hd), "dO is read token-major where it lies"
+            names = {n.arg.name for n in layer_gradient(limn.float32) if n.op is Op.CUSTOM}
+            assert names == {"sdpa", "sdpa_bwd_q", "sdpa_bwd_kv"}, "float32 is not served strided: limn's own path"
+        finally:
+            device_module.DEVICES["c"] = original
+            limn.set_device("numpy")
+            undo()
+        assert not getattr(limn.Tensor.attention, "_limn_b200_views", False)
     finally:
         sys.path.remove(str(REFERENCE))

@@ -281,6 +281,56 @@ def test_the_frontend_patch_for_the_fused_row_dot(limn):
             np.testing.assert_allclose(g, w, rtol=3e-2, atol=3e-2)
 
 
+def test_attention_over_views_in_place(limn):
+    """limn_b200.frontend.read_views_in_place(): an attention layer as a model writes it (one projection, q, k, v as
+    slices of it, the result permuted back for the output projection) on limn's cuda device: the gradient with
+    respect to the projection matches limn's numpy device, the plan has no copy kernel per operand any more, and the
+    strided Runners are what ran."""
+    import limn_b200
+    from limn_b200 import frontend as patch
+
+    b, t, heads, hd = 2, 200, 3, 64
+    data = rng.standard_normal((b, t, 3 * heads * hd)).astype(np.float32)
+    weight = rng.standard_normal((b, t, heads * hd)).astype(np.float32)
+
+    def layer_gradient(device_name: str):
+        limn.device.set_device(device_name)
+        try:
+            dev = limn.device.active()
+            ran = []
+            if device_name == "cuda":
+                limn_b200.install(dev)
+                for name in list(dev.custom):
+                    build = dev.custom[name]
+                    dev.custom[name] = lambda node, build=build, name=name: (ran.append(name), build(node))[1]
+            x = limn.Tensor(data, requires_grad=True)
+            q, k, v = x.cast(limn.bfloat16).reshape(b, t, 3, heads, hd).permute(2, 0, 3, 1, 4)
+            y = q.attention(k, v, causal=True).permute(0, 2, 1, 3).reshape(b, t, heads * hd).cast(limn.float32)
+            (g,) = limn.grad((y * limn.Tensor(weight)).sum(), [x])
+            calls = None
+            if device_name == "cuda":
+                limn.realize(y, g)
+                calls = max(len(plan.calls) for plan in dev.plans.values())
+            return y.numpy(), g.numpy(), calls, ran
+        finally:
+            limn.device.set_device("numpy")
+
+    want_y, want_g, _, _ = layer_gradient("numpy")
+    plain_y, plain_g, plain_calls, plain_ran = layer_gradient("cuda")
+    undo = patch.read_views_in_place()
+    try:
+        got_y, got_g, got_calls, got_ran = layer_gradient("cuda")
+    finally:
+        undo()
+    assert set(got_ran) == {"sdpa_strided", "sdpa_bwd_q_fused_strided", "sdpa_bwd_kv_strided"}, got_ran
+    assert set(plain_ran) == {"sdpa", "sdpa_bwd_q", "sdpa_bwd_kv"}, plain_ran
+    assert got_calls <= plain_calls - 4, (got_calls, plain_calls)  # three operand copies, the dO copy, the row dot ...
+    for got, want in ((plain_y, want_y), (got_y, want_y)):
+        np.testing.assert_allclose(got, want, rtol=2e-2, atol=2e-2)
+    for got, want in ((plain_g, want_g), (got_g, want_g)):
+        np.testing.assert_allclose(got, want, rtol=3e-2, atol=3e-2)
+
+
 def test_a_gpt_training_step_under_capture(limn):
     """The caller of the GPT attention layer: a two-layer byte-level GPT step shaped like limn's
     examples/train_stories.py (its model and step, :26-56 and :140-147 there) with bfloat16 attention operands,
