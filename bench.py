@@ -897,6 +897,27 @@ def limn_arm(workload: str) -> None:
             entry["fwd_bwd_ms"], entry["fwd_bwd_tflops"] = ms, 3.5 * fwd_flops(problems, s, d, causal) / (ms * 1e-3) / 1e12
         return entry
 
+    def layer_case(reps: int) -> dict:
+        """The attention of one gpt_layer-sized transformer layer as a model holds it: q, k, v are slices of one
+        bfloat16 projection output (batch, t, 3 * heads * hd), the result goes back to (batch, t, heads * hd); forward
+        plus the gradient with respect to the projection. What differs between the columns is what limn puts around
+        the three kernels: copies of q, k, v and dO and the row-dot reduce, or nothing."""
+        b, h, s, d, causal, *_ = WORKLOADS["gpt_layer"]
+        data = (rng.standard_normal((b, s, 3 * h * d)).astype(np.float32)).astype(BF16)
+        weight = rng.standard_normal((b, s, h * d)).astype(np.float32).astype(BF16)
+
+        def step(x, w):
+            q, k, v = x.reshape(b, s, 3, h, d).permute(2, 0, 3, 1, 4)
+            y = q.attention(k, v, causal=causal).permute(0, 2, 1, 3).reshape(b, s, h * d)
+            (g,) = limn.grad((y * w).sum(), [x])
+            limn.realize(y, g)
+            return y, g
+
+        args = (limn.Tensor(data, requires_grad=True), limn.Tensor(weight))
+        ms = replay_ms(step, args, reps)
+        return {"ms": ms, "fwd_bwd_tflops": 3.5 * fwd_flops(b * h, s, d, causal) / (ms * 1e-3) / 1e12,
+                "what": "attention of one layer from its projection output to its result and back, B=32 H=8 S=256 D=64 causal bf16"}
+
     def gpt_case(reps: int, cast_in_place: bool = False) -> dict:
         ctx, batch = 256, 32
         limn.set_seed(0)
@@ -925,6 +946,7 @@ def limn_arm(workload: str) -> None:
             found[label][workload] = attention_case(workload, 16, 3)
             if workload != "gpt_layer":
                 found[label]["gpt_layer"] = attention_case("gpt_layer", 256, 10)
+            found[label]["gpt_layer_from_projection"] = layer_case(10)
             found[label]["gpt_train_step"] = gpt_case(5, cast_in_place=patched)
         except Exception as err:
             found[label]["error"] = f"{type(err).__name__}: {err}"[:300]
