@@ -913,7 +913,7 @@ def limn_arm(workload: str) -> None:
             limn.realize(y, g)
             return y, g
 
-        args = (limn.Tensor(data, requires_grad=True), limn.Tensor(weight))
+        args = (limn.Tensor(data.astype(np.float32), dtype=limn.bfloat16, requires_grad=True), limn.Tensor(weight.astype(np.float32), dtype=limn.bfloat16))
         ms = replay_ms(step, args, reps)
         return {"ms": ms, "fwd_bwd_tflops": 3.5 * fwd_flops(b * h, s, d, causal) / (ms * 1e-3) / 1e12,
                 "what": "attention of one layer from its projection output to its result and back, B=32 H=8 S=256 D=64 causal bf16"}

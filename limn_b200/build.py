@@ -21,7 +21,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OBJ = HERE / "build"
 LIB = HERE / "liblimn_b200.so"
-SOURCES = ["capi.cu", "sdpa_general.cu", "dispatch_sm100.cu", "sdpa_fwd_sm100.cu", "sdpa_bwd_sm100.cu", "sdpa_decode.cu", "static_scratch.cu", "wait_probe.cu", "nccl_gather.cpp"]
+SOURCES = ["capi.cu", "sdpa_general.cu", "sdpa_general_tiled.cu", "dispatch_sm100.cu", "sdpa_fwd_sm100.cu", "sdpa_bwd_sm100.cu", "sdpa_decode.cu", "static_scratch.cu", "wait_probe.cu", "nccl_gather.cpp"]
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC", "-Xptxas", "-v",

@@ -1,7 +1,9 @@
 // General fused-attention kernels: any float storage type, any head dims, optional key mask,
 // rectangular t_q x t_k. These serve every problem the tcgen05 kernels do not take
 // (float32 and float64 in particular, which have to be computed at their own width to meet
-// the reference's 1e-5 / 1e-12 checks: tests/test_attention.py:250-255, limn/sdpa.py:279-291).
+// the reference's 1e-5 / 1e-12 checks: tests/test_attention.py:250-255, limn/sdpa.py:279-291);
+// the tiled kernels of sdpa_general_tiled.cu take over where a problem fills their tiles, and
+// what stays here is float64, head dims above 128 and sides shorter than 16 rows.
 //
 // Shape of the work: one warp owns one row for the whole pass (a query row in the forward
 // and the dQ pass, a key row in the dK/dV pass), so every total has exactly one owner, no
@@ -406,6 +408,7 @@ int launch_width(Op op, const Problem& p) {
 }  // namespace
 
 int general_launch(Op op, const Problem& p) {
+  if (general_tiled_serves(op, p)) return general_tiled_launch(op, p);
   switch (p.dtype) {
     case LIMN_B200_F32: return launch_width<float, float>(op, p);
     case LIMN_B200_F16: return launch_width<__half, float>(op, p);

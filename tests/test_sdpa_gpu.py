@@ -178,6 +178,83 @@ def test_masked_row_without_a_visible_key_on_the_tensor_core_path(dev):
     assert float(np.abs(lse[:, 5:] - want_lse[:, 5:]).max()) <= 1e-3
 
 
+TILED_CASES = [
+    # id, dtype, q, k, v shapes, causal, mask kind
+    ("f32 d64 causal 256 batch (a GPT layer in float32)", np.float32, (4, 8, 256, 64), (4, 8, 256, 64), (4, 8, 256, 64), True, None),
+    ("f32 d128 causal ragged 1000", np.float32, (2, 1000, 128), (2, 1000, 128), (2, 1000, 128), True, None),
+    ("f32 d37 full 131 (rows that are no whole 16-byte pieces)", np.float32, (3, 131, 37), (3, 131, 37), (3, 131, 37), False, None),
+    ("f32 d40 hd_v 24 rect 70x333", np.float32, (2, 70, 40), (2, 333, 40), (2, 333, 24), False, None),
+    ("f32 d64 causal, keys hidden at random", np.float32, (2, 2, 257, 64), (2, 2, 257, 64), (2, 2, 257, 64), True, "holes"),
+    ("f32 d128 full, padded batch", np.float32, (3, 200, 128), (3, 200, 128), (3, 200, 128), False, "pad"),
+    ("f32 d32 rect 16x16 (the smallest tiled sides)", np.float32, (5, 16, 32), (5, 16, 32), (5, 16, 32), False, None),
+    ("f16 d96 causal 300", np.float16, (2, 300, 96), (2, 300, 96), (2, 300, 96), True, None),
+    ("bf16 d32 full 500, padded batch", BF16, (2, 500, 32), (2, 500, 32), (2, 500, 32), False, "pad"),
+    ("bf16 hd 128 hd_v 64 rect 100x260", BF16, (2, 100, 128), (2, 260, 128), (2, 260, 64), False, None),
+]
+
+
+@pytest.mark.parametrize("case", TILED_CASES, ids=[c[0] for c in TILED_CASES])
+def test_tiled_general_kernels_match_oracle(case, dev):
+    """What the tensor-core kernels do not take and still fills a tile: float32 at its own width, head dims other
+    than 64 and 128 up to 128, hd != hd_v; with masks, ragged and rectangular sides. Hidden keys get exact-zero
+    dK and dV, and a second run gives the same bits (one owner per total, fixed summation order)."""
+    import limn_standin as host
+    from limn_b200._lib import PATH_GENERAL, lib
+
+    _, dtype, qs, ks, vs, causal, kind = case
+    name = "bfloat16" if dtype == BF16 else np.dtype(dtype).name
+    code = {"float32": 0, "float16": 1, "bfloat16": 2}[name]
+    assert lib().limn_b200_sdpa_path(code, int(np.prod(qs[:-2])), qs[-2], ks[-2], qs[-1], vs[-1], int(causal), int(kind is not None), qs[-1] ** -0.5) == PATH_GENERAL
+    q, k, v, do = _random_case(300 + qs[-2] + qs[-1], dtype, qs, ks, vs)
+    mask = None
+    if kind is not None:
+        rng = np.random.default_rng(qs[-2])
+        t_k = ks[-2]
+        if kind == "holes":
+            mask = (rng.random(ks[:-1]) > 0.3).astype(np.float32)
+            mask[..., 0] = 1  # under causal, row 0 sees key 0 only
+        else:
+            mask = np.broadcast_to((np.arange(t_k) < t_k * 2 // 3).astype(np.float32), ks[:-1]).copy()
+        mask = mask.astype(dtype)
+    scale = qs[-1] ** -0.5
+    att = host.Attention(dev, q, k, v, causal=causal, key_mask=mask)
+    out, lse = att.forward()
+    want_out, want_lse = oracle.sdpa_forward(q, k, v, mask, causal=causal, scale=scale)
+    close(out, want_out, FWD_TOL[name], "O")
+    close(lse, want_lse, LSE_TOL, "L")
+    dq, dk, dv = att.backward(do)
+    delta = oracle.row_delta(do, want_out)
+    want_dq = oracle.sdpa_backward_q(q, k, v, do, want_lse, delta, mask, causal=causal, scale=scale)
+    want_dk, want_dv = oracle.sdpa_backward_kv(q, k, v, do, want_lse, delta, mask, causal=causal, scale=scale)
+    for got, want, what in ((dq, want_dq, "dQ"), (dk, want_dk, "dK"), (dv, want_dv, "dV")):
+        close(got, want, BWD_TOL[name], what)
+    if mask is not None:
+        hidden = mask.astype(np.float32) == 0
+        assert (dk.astype(np.float32)[hidden] == 0).all() and (dv.astype(np.float32)[hidden] == 0).all()
+    again = host.Attention(dev, q, k, v, causal=causal, key_mask=mask)
+    out2, lse2 = again.forward()
+    assert out2.tobytes() == out.tobytes() and lse2.tobytes() == lse.tobytes()
+    for first, second in zip((dq, dk, dv), again.backward(do)):
+        assert first.tobytes() == second.tobytes()
+
+
+def test_tiled_general_kernels_on_rows_without_a_visible_key(dev):
+    """float32, causal with the first 5 keys hidden: rows 0-4 see nothing and come back NaN with L = -inf, the
+    rest are ordinary, and dQ of the empty rows is zero (limn/sdpa.py:111-112)."""
+    import limn_standin as host
+
+    rng = np.random.default_rng(78)
+    q, k, v, do = (rng.standard_normal((2, 200, 64)).astype(np.float32) for _ in range(4))
+    mask = np.ones((2, 200), np.float32)
+    mask[:, :5] = 0
+    att = host.Attention(dev, q, k, v, causal=True, key_mask=mask)
+    out, lse = att.forward()
+    want_out, want_lse = oracle.sdpa_forward(q, k, v, mask, causal=True, scale=0.125)
+    assert np.isnan(out[:, :5]).all() and np.isneginf(lse[:, :5]).all()
+    assert oracle.worst(out[:, 5:], want_out[:, 5:]) <= 1e-4
+    assert float(np.abs(lse[:, 5:] - want_lse[:, 5:]).max()) <= 1e-3
+
+
 FUSED_CASES = [
     # id, dtype, code, shape (q = k = v), causal, key mask?, layout
     ("bf16 d128 causal", BF16, 2, (3, 384, 128), True, False, "bhtd"),
