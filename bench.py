@@ -548,38 +548,43 @@ def decode_cases(args, world: int, torch, device, barrier, max_over_ranks) -> di
     return found
 
 
-def float32_cases(args, world: int, torch, device, barrier, max_over_ranks) -> dict:
-    """float32 storage, which the ops compute at float32 on the CUDA cores (limn's numpy and c devices run
-    BASELINE's first configuration this way, and a model kept in float32 calls the ops like this): forward and
-    forward+backward with the row dot as its own launch, against the float32 multiply-add rate of the part
-    (SMs x 128 lanes x 2 x the sampled maximum SM clock: a nominal figure, nothing measures it here)."""
+def off_grid_cases(args, world: int, torch, device, barrier, max_over_ranks) -> dict:
+    """Shapes outside the four BASELINE configurations that the ops are still called with, device-resident, forward and
+    forward+backward (row dot as its own launch). "float32": float32 storage, computed at float32 on the CUDA cores
+    (limn's numpy and c devices run BASELINE's first configuration this way, and a model kept in float32 calls the
+    ops like this), against the float32 multiply-add rate of the part (SMs x 128 lanes x 2 x the maximum SM clock: a
+    nominal figure, nothing measures it here). "narrow_heads": bfloat16 with head dims that are not 64 or 128, which
+    run zero-padded in the tensor-core kernels; credited with the flops of the real head dim."""
     from limn_b200._lib import lib
 
     L = lib()
     props = torch.cuda.get_device_properties(device)
     fma_peak = props.multi_processor_count * 128 * 2 * 1.965e9 / 1e12
-    found = {"fp32_fma_tflops_nominal": fma_peak}
-    cases = (("reference_cpu_case_B1_H2_S128_D32_causal", 2, 128, 32, True), ("gpt_layer_in_float32_B32_H8_S256_D64_causal", 256, 256, 64, True),
-             ("B4_H16_S1024_D128_causal", 64, 1024, 128, True))
-    for name, bh_all, s, d, causal in cases:
+    found = {"float32": {"fp32_fma_tflops_nominal": fma_peak}, "narrow_heads": {}}
+    cases = (("float32", "reference_cpu_case_B1_H2_S128_D32_causal", 2, 128, 32, True),
+             ("float32", "gpt_layer_in_float32_B32_H8_S256_D64_causal", 256, 256, 64, True),
+             ("float32", "B4_H16_S1024_D128_causal", 64, 1024, 128, True),
+             ("narrow_heads", "bf16_B8_H16_S2048_D96_causal", 128, 2048, 96, True),
+             ("narrow_heads", "bf16_B32_H8_S256_D32_causal", 256, 256, 32, True))
+    for family, name, bh_all, s, d, causal in cases:
         bh = max(1, bh_all // world)
-        q, k, v, do = (torch.randn((bh, s, d), device=device) for _ in range(4))
+        f32 = family == "float32"
+        code = 0 if f32 else 2
+        q, k, v, do = (torch.randn((bh, s, d), device=device).to(torch.float32 if f32 else torch.bfloat16) for _ in range(4))
         out, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
         lse, delta = (torch.empty((bh, s), dtype=torch.float32, device=device) for _ in range(2))
-        tail = (0, bh, s, s, d, d, int(causal), d ** -0.5, None)
-        count = [0]
+        tail = (code, bh, s, s, d, d, int(causal), d ** -0.5, None)
 
-        def check(code):
-            if code:
+        def check(status):
+            if status:
                 raise RuntimeError(L.limn_b200_last_error().decode())
-            count[0] += L.limn_b200_last_launch_count()
 
         def forward():
             check(L.limn_b200_sdpa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), None, out.data_ptr(), lse.data_ptr(), *tail))
 
         def step():
             forward()
-            check(L.limn_b200_sdpa_delta(out.data_ptr(), do.data_ptr(), delta.data_ptr(), 0, bh * s, d, None))
+            check(L.limn_b200_sdpa_delta(out.data_ptr(), do.data_ptr(), delta.data_ptr(), code, bh * s, d, None))
             check(L.limn_b200_sdpa_bwd_q(q.data_ptr(), k.data_ptr(), v.data_ptr(), do.data_ptr(), lse.data_ptr(), delta.data_ptr(), None, dq.data_ptr(), *tail))
             check(L.limn_b200_sdpa_bwd_kv(q.data_ptr(), k.data_ptr(), v.data_ptr(), do.data_ptr(), lse.data_ptr(), delta.data_ptr(), None, dk.data_ptr(), dv.data_ptr(), *tail))
 
@@ -592,11 +597,12 @@ def float32_cases(args, world: int, torch, device, barrier, max_over_ranks) -> d
                 barrier()
                 trials.append(max_over_ranks(timed(None, 10, body)) / 10)
             ms = min(trials)
-            tflops = credit * fwd_flops(bh * world, s, d, causal) / (ms * 1e-3) / 1e12
-            executed = (1.0 if key == "fwd" else 4.5) * fwd_flops(bh, s, d, causal) / (ms * 1e-3) / 1e12
-            entry[key + "_ms"], entry[key + "_tflops"] = ms, tflops
-            entry[key + "_executed_frac_of_fp32_fma_nominal"] = executed / fma_peak
-        found[name] = entry
+            entry[key + "_ms"] = ms
+            entry[key + "_tflops"] = credit * fwd_flops(bh * world, s, d, causal) / (ms * 1e-3) / 1e12
+            if f32:
+                executed = (1.0 if key == "fwd" else 4.5) * fwd_flops(bh, s, d, causal) / (ms * 1e-3) / 1e12
+                entry[key + "_executed_frac_of_fp32_fma_nominal"] = executed / fma_peak
+        found[family][name] = entry
     return found
 
 
@@ -766,7 +772,7 @@ def gpu_arm(args) -> None:
     others = other_workloads(args, workload, world, rank, torch, device, barrier, max_over_ranks) if args.others else None
     if others is not None:
         others["decode"] = decode_cases(args, world, torch, device, barrier, max_over_ranks)
-        others["float32"] = float32_cases(args, world, torch, device, barrier, max_over_ranks)
+        others.update(off_grid_cases(args, world, torch, device, barrier, max_over_ranks))
 
     status = runtime.device_status()
     if status:

@@ -9,7 +9,8 @@ int tcgen05_bwd_kv(const Problem& p);
 
 bool tcgen05_serves(Op op, const Problem& p) {
   if (p.dtype != LIMN_B200_BF16 && p.dtype != LIMN_B200_F16) return false;
-  if (p.hd != p.hd_v || (p.hd != 64 && p.hd != 128)) return false;
+  // built for head dims 64 and 128; a narrower head runs in the next of the two with its missing columns read as zeros
+  if (p.hd != p.hd_v || p.hd < 8 || p.hd > 128 || p.hd % 8 != 0) return false;
   if (!(p.scale > 0.0)) return false;          // the softmax folds the scale into exp2 and takes row maxima before scaling
   if (p.bh > 0x7fffffffLL) return false;       // problem index is a 32-bit TMA coordinate
   return true;

@@ -1,4 +1,5 @@
-// "sdpa_bwd_q" and "sdpa_bwd_kv" for f16/bf16 with hd == hd_v in {64, 128}: TMA-staged
+// "sdpa_bwd_q" and "sdpa_bwd_kv" for f16/bf16 with hd == hd_v a multiple of 8 up to 128 (kernels for 64 and 128; a
+// narrower head runs in the next of the two, its missing columns read as zeros by TMA and never stored): TMA-staged
 // tiles, tcgen05 MMAs accumulating in tensor memory, probabilities rebuilt from the saved
 // log-sum-exp. Two separate passes, as in the kernels these replace (limn/cuda_emit.py:968-1083):
 // every dQ row and every dK/dV row has one owning CTA and is accumulated in a fixed order,
@@ -137,6 +138,7 @@ struct BwdParams {
   Strides o_strides, do_strides;  // fused dQ pass: of the rows of O and dO the row statistic is computed from
   unsigned items;      // work items: bh * (tiles of 128 rows a problem's owner side has)
   int t_q, t_k;
+  int width;           // head dim of the operands as they lie in memory (<= D): TMA zero-fills the rest, stores skip it
   int q_tiles, kv_tiles;
   float scale;
 };
@@ -144,9 +146,10 @@ struct BwdParams {
 // barrier among the 128 threads of one group (ids 1 and 2; 0 is __syncthreads)
 __device__ __forceinline__ void group_barrier(int group) { asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory"); }
 
-// One accumulator row slice (32 fp32 columns) scaled, rounded and written as 64 bytes.
+// One accumulator row slice (32 fp32 columns) scaled, rounded and written as 64 bytes, or as many 16-byte pieces
+// of them as the row has columns left.
 template <bool kFp16>
-__device__ __forceinline__ void store_row32(void* base, long long elem_offset, const uint32_t (&acc)[32], float mul) {
+__device__ __forceinline__ void store_row32(void* base, long long elem_offset, const uint32_t (&acc)[32], float mul, int cols_left) {
   uint4* dst = reinterpret_cast<uint4*>(static_cast<unsigned char*>(base) + elem_offset * 2);
 #pragma unroll
   for (int v4 = 0; v4 < 4; ++v4) {
@@ -157,19 +160,20 @@ __device__ __forceinline__ void store_row32(void* base, long long elem_offset, c
       const float b = __uint_as_float(acc[v4 * 8 + 2 * i + 1]) * mul;
       w[i] = kFp16 ? pack_f16(a, b) : pack_bf16(a, b);
     }
-    dst[v4] = make_uint4(w[0], w[1], w[2], w[3]);
+    if (8 * v4 < cols_left) dst[v4] = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
 
-// sum_d a[d] * b[d] over one row of D 16-bit elements each, in fp32 (four partial sums): the delta of one query
-// row from its O and dO rows (limn/tensor.py:705-706).
+// sum_d a[d] * b[d] over one row of `pieces` * 8 <= D 16-bit elements each, in fp32 (four partial sums): the delta
+// of one query row from its O and dO rows (limn/tensor.py:705-706).
 template <int D, bool kFp16>
-__device__ __forceinline__ float row_dot(const void* a_row, const void* b_row) {
+__device__ __forceinline__ float row_dot(const void* a_row, const void* b_row, int pieces) {
   const uint4* a = static_cast<const uint4*>(a_row);
   const uint4* b = static_cast<const uint4*>(b_row);
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int i = 0; i < D / 8; ++i) {
+    if (i >= pieces) break;
     const uint4 x = a[i], y = b[i];
     const uint32_t xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
 #pragma unroll
@@ -804,7 +808,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           uint32_t acc[32];
           tmem_ld32(t_acc + 32 * c, acc);
           tmem_ld_wait();
-          if (in) store_row32<kFp16>(dst, out_at + 32 * c, acc, mul);
+          if (in) store_row32<kFp16>(dst, out_at + 32 * c, acc, mul, prm.width - 32 * c);
         }
       } else {
         // each group writes half of this query's dQ row
@@ -816,7 +820,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           uint32_t acc[32];
           tmem_ld32(tmem + lane_base + L::kAcc0 + col, acc);
           tmem_ld_wait();
-          if (in) store_row32<kFp16>(prm.out0, out_at + col, acc, prm.scale);
+          if (in) store_row32<kFp16>(prm.out0, out_at + col, acc, prm.scale, prm.width - col);
         }
       }
       // the accumulators are in registers or stored: the next item's first products may overwrite them
@@ -851,7 +855,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const int row = min(item.own0 + local, prm.t_q - 1);
         const long long o_at = (item.batch * prm.o_strides.batch + item.head * prm.o_strides.head + row * prm.o_strides.row) * 2;
         const long long do_at = (item.batch * prm.do_strides.batch + item.head * prm.do_strides.head + row * prm.do_strides.row) * 2;
-        const float d = row_dot<D, kFp16>(static_cast<const unsigned char*>(prm.o_rows) + o_at, static_cast<const unsigned char*>(prm.do_rows) + do_at);
+        const float d = row_dot<D, kFp16>(static_cast<const unsigned char*>(prm.o_rows) + o_at, static_cast<const unsigned char*>(prm.do_rows) + do_at, prm.width >> 3);
         delta_ring[slot][local] = d;
         if (item.own0 + local < prm.t_q) prm.delta_out[static_cast<long long>(item.problem) * prm.t_q + row] = d;
       }
@@ -884,10 +888,10 @@ int launch_bwd(const Problem& p) {
   using L = BwdLayout<D, kKV, kMask>;
   CUtensorMap map_q, map_k, map_v, map_do;
   const int heads = p.heads > 0 ? p.heads : static_cast<int>(p.bh), batch = static_cast<int>(p.bh / heads);
-  if (int rc = make_tile_map(&map_q, p.q, kFp16, batch, heads, p.t_q, D, kTile, operand_strides(p, kOpQ, heads, p.t_q, D))) return rc;
-  if (int rc = make_tile_map(&map_k, p.k, kFp16, batch, heads, p.t_k, D, kTile, operand_strides(p, kOpK, heads, p.t_k, D))) return rc;
-  if (int rc = make_tile_map(&map_v, p.v, kFp16, batch, heads, p.t_k, D, kTile, operand_strides(p, kOpV, heads, p.t_k, D))) return rc;
-  if (int rc = make_tile_map(&map_do, p.dout, kFp16, batch, heads, p.t_q, D, kTile, operand_strides(p, kOpDout, heads, p.t_q, D))) return rc;
+  if (int rc = make_tile_map(&map_q, p.q, kFp16, batch, heads, p.t_q, p.hd, kTile, operand_strides(p, kOpQ, heads, p.t_q, p.hd))) return rc;
+  if (int rc = make_tile_map(&map_k, p.k, kFp16, batch, heads, p.t_k, p.hd, kTile, operand_strides(p, kOpK, heads, p.t_k, p.hd))) return rc;
+  if (int rc = make_tile_map(&map_v, p.v, kFp16, batch, heads, p.t_k, p.hd, kTile, operand_strides(p, kOpV, heads, p.t_k, p.hd))) return rc;
+  if (int rc = make_tile_map(&map_do, p.dout, kFp16, batch, heads, p.t_q, p.hd, kTile, operand_strides(p, kOpDout, heads, p.t_q, p.hd))) return rc;
   BwdParams prm;
   prm.mask = static_cast<const unsigned short*>(p.mask);
   prm.lse = static_cast<const float*>(p.lse_in);
@@ -898,10 +902,10 @@ int launch_bwd(const Problem& p) {
   prm.out0 = kKV ? p.dk : p.dq;
   prm.out1 = kKV ? p.dv : nullptr;
   prm.heads = heads;
-  prm.out_strides = kKV ? operand_strides(p, kOpDk, heads, p.t_k, D) : operand_strides(p, kOpDq, heads, p.t_q, D);
-  prm.out1_strides = operand_strides(p, kOpDv, heads, p.t_k, D);
-  prm.o_strides = operand_strides(p, kOpOut, heads, p.t_q, D);
-  prm.do_strides = operand_strides(p, kOpDout, heads, p.t_q, D);
+  prm.out_strides = kKV ? operand_strides(p, kOpDk, heads, p.t_k, p.hd) : operand_strides(p, kOpDq, heads, p.t_q, p.hd);
+  prm.out1_strides = operand_strides(p, kOpDv, heads, p.t_k, p.hd);
+  prm.o_strides = operand_strides(p, kOpOut, heads, p.t_q, p.hd);
+  prm.do_strides = operand_strides(p, kOpDout, heads, p.t_q, p.hd);
   {
     const long long all = prm.out_strides.batch | prm.out_strides.head | prm.out_strides.row | prm.out1_strides.batch |
                           prm.out1_strides.head | prm.out1_strides.row | prm.o_strides.batch | prm.o_strides.head | prm.o_strides.row;
@@ -914,6 +918,7 @@ int launch_bwd(const Problem& p) {
     if (int rc = status_word(&prm.status)) return rc;
   prm.bh = p.bh;
   prm.t_q = p.t_q, prm.t_k = p.t_k;
+  prm.width = p.hd;
   prm.q_tiles = (p.t_q + kTile - 1) / kTile;
   prm.kv_tiles = (p.t_k + kTile - 1) / kTile;
 #ifdef LIMN_TRACE
@@ -962,7 +967,7 @@ int launch_bwd_d(const Problem& p) {
 
 }  // namespace
 
-int tcgen05_bwd_q(const Problem& p) { return p.hd == 128 ? launch_bwd_d<128, false>(p) : launch_bwd_d<64, false>(p); }
-int tcgen05_bwd_kv(const Problem& p) { return p.hd == 128 ? launch_bwd_d<128, true>(p) : launch_bwd_d<64, true>(p); }
+int tcgen05_bwd_q(const Problem& p) { return p.hd > 64 ? launch_bwd_d<128, false>(p) : launch_bwd_d<64, false>(p); }
+int tcgen05_bwd_kv(const Problem& p) { return p.hd > 64 ? launch_bwd_d<128, true>(p) : launch_bwd_d<64, true>(p); }
 
 }  // namespace limn_b200

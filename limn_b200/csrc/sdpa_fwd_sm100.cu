@@ -1,5 +1,7 @@
-// "sdpa" forward for f16/bf16 with hd == hd_v in {64, 128}, with or without a key mask: TMA-staged tiles, tcgen05 MMAs
-// accumulating in tensor memory, online softmax with one thread per query row.
+// "sdpa" forward for f16/bf16 with hd == hd_v a multiple of 8 up to 128, with or without a key mask: TMA-staged tiles,
+// tcgen05 MMAs accumulating in tensor memory, online softmax with one thread per query row. The kernels are built for
+// head dims 64 and 128; a narrower head runs in the next of the two: TMA fills the columns a row does not have with
+// zeros, which add nothing to a score and give zero output columns that are not stored.
 //
 // A work item is two consecutive tiles of 128 query rows of one (batch, head) problem; the problem's keys
 // and values stream past them in tiles of 128 keys:
@@ -118,6 +120,7 @@ struct FwdParams {
   Strides out_strides; // of O, in elements
   unsigned items;      // work items: bh * q_pairs
   int t_q, t_k;
+  int width;        // head dim of the operands as they lie in memory (<= D)
   int q_pairs;      // work items per problem
   int kv_tiles;     // ceil(t_k / 128)
   float scale;
@@ -546,7 +549,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
               const float b = __uint_as_float(o[v4 * 8 + 2 * i + 1]) * inv;
               w[i] = kFp16 ? pack_f16(a, b) : pack_bf16(a, b);
             }
-            dst[v4] = make_uint4(w[0], w[1], w[2], w[3]);
+            if (32 * c + 8 * v4 < prm.width) dst[v4] = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
       }
@@ -584,13 +587,14 @@ int launch_fwd(const Problem& p) {
   using L = FwdLayout<D>;
   CUtensorMap map_q, map_k, map_v;
   const int heads = p.heads > 0 ? p.heads : static_cast<int>(p.bh), batch = static_cast<int>(p.bh / heads);
-  if (int rc = make_tile_map(&map_q, p.q, kFp16, batch, heads, p.t_q, D, kTileRows, operand_strides(p, kOpQ, heads, p.t_q, D))) return rc;
-  if (int rc = make_tile_map(&map_k, p.k, kFp16, batch, heads, p.t_k, D, kTileRows, operand_strides(p, kOpK, heads, p.t_k, D))) return rc;
-  if (int rc = make_tile_map(&map_v, p.v, kFp16, batch, heads, p.t_k, D, kTileRows, operand_strides(p, kOpV, heads, p.t_k, D))) return rc;
+  if (int rc = make_tile_map(&map_q, p.q, kFp16, batch, heads, p.t_q, p.hd, kTileRows, operand_strides(p, kOpQ, heads, p.t_q, p.hd))) return rc;
+  if (int rc = make_tile_map(&map_k, p.k, kFp16, batch, heads, p.t_k, p.hd, kTileRows, operand_strides(p, kOpK, heads, p.t_k, p.hd))) return rc;
+  if (int rc = make_tile_map(&map_v, p.v, kFp16, batch, heads, p.t_k, p.hd, kTileRows, operand_strides(p, kOpV, heads, p.t_k, p.hd))) return rc;
   FwdParams prm;
   prm.out = p.out;
   prm.heads = heads;
-  prm.out_strides = operand_strides(p, kOpOut, heads, p.t_q, D);
+  prm.out_strides = operand_strides(p, kOpOut, heads, p.t_q, p.hd);
+  prm.width = p.hd;
   if ((prm.out_strides.batch | prm.out_strides.head | prm.out_strides.row) & 7)
     return fail(LIMN_B200_BAD_ARGUMENT, "sdpa: operand strides must be multiples of 8 elements");
   if (reinterpret_cast<uintptr_t>(p.out) & 15u) return fail(LIMN_B200_BAD_ARGUMENT, "sdpa: the output is not 16-byte aligned");
@@ -647,6 +651,6 @@ int launch_fwd_d(const Problem& p) {
 
 }  // namespace
 
-int tcgen05_fwd(const Problem& p) { return p.hd == 128 ? launch_fwd_d<128>(p) : launch_fwd_d<64>(p); }
+int tcgen05_fwd(const Problem& p) { return p.hd > 64 ? launch_fwd_d<128>(p) : launch_fwd_d<64>(p); }
 
 }  // namespace limn_b200

@@ -285,17 +285,20 @@ row_dot_kernel(const T* __restrict__ out, const T* __restrict__ dout, C* __restr
 
 // The same row dot for 2-byte storage when a row is a whole number of 16-byte pieces: each
 // thread takes 8 elements of one row with one 16-byte load from each tensor, and the
-// threads of a row (hd_v / 8 of them, a power of two up to 32, consecutive lanes) fold their
-// partial sums with shuffles. Both tensors are read exactly once at full sector width, so the
-// kernel runs at memory speed; the generic kernel above serves every other shape.
+// threads of a row (kLanes of them, the power of two that holds the row's hd_v / 8 pieces, consecutive
+// lanes; those beyond the row's pieces idle) fold their partial sums with shuffles. Both tensors are read
+// exactly once at full sector width, so the kernel runs at memory speed; the generic kernel above serves
+// every other shape.
 template <bool kFp16, int kLanes>
 __global__ void __launch_bounds__(256)
 row_dot16_kernel(const uint4* __restrict__ out, const uint4* __restrict__ dout, float* __restrict__ delta,
-                 long long rows, int heads, int t) {
-  const long long piece = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;  // 16-byte piece index
-  const long long row = piece / kLanes;
+                 long long rows, int pieces, int heads, int t) {
+  const long long slot = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long row = slot / kLanes;
+  const int within = static_cast<int>(slot - row * kLanes);
   float acc = 0.f;
-  if (row < rows) {
+  if (row < rows && within < pieces) {
+    const long long piece = row * pieces + within;  // 16-byte piece index
     const uint4 a = out[piece], b = dout[piece];
     const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
@@ -315,7 +318,7 @@ row_dot16_kernel(const uint4* __restrict__ out, const uint4* __restrict__ dout, 
   }
 #pragma unroll
   for (int off = kLanes / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(kFull, acc, off);
-  if (row < rows && (threadIdx.x & (kLanes - 1)) == 0) {
+  if (row < rows && within == 0) {
     long long to = row;
     if (heads > 0) {
       // rows lie in memory as (batch, t, head); delta is (batch, head, t)
@@ -331,22 +334,24 @@ row_dot16_kernel(const uint4* __restrict__ out, const uint4* __restrict__ dout, 
 template <bool kFp16>
 bool launch_row_dot16(const void* out, const void* dout, void* delta, long long rows, int hd_v, cudaStream_t stream,
                       int heads = 0, int t = 0) {
-  const int lanes = hd_v / 8;
-  if (hd_v % 8 != 0 || lanes > 32 || (lanes & (lanes - 1)) != 0) return false;
+  const int pieces = hd_v / 8;
+  if (hd_v % 8 != 0 || pieces > 32) return false;
   if ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(dout)) & 15u) return false;
-  const long long pieces = rows * lanes;
-  const long long blocks = (pieces + 255) / 256;
+  int lanes = 1;
+  while (lanes < pieces) lanes *= 2;
+  const long long slots = rows * lanes;
+  const long long blocks = (slots + 255) / 256;
   if (blocks > 0x7fffffffLL) return false;
   const dim3 grid(static_cast<unsigned>(blocks)), block(256);
   auto a = static_cast<const uint4*>(out), b = static_cast<const uint4*>(dout);
   auto d = static_cast<float*>(delta);
   switch (lanes) {
-    case 1: row_dot16_kernel<kFp16, 1><<<grid, block, 0, stream>>>(a, b, d, rows, heads, t); break;
-    case 2: row_dot16_kernel<kFp16, 2><<<grid, block, 0, stream>>>(a, b, d, rows, heads, t); break;
-    case 4: row_dot16_kernel<kFp16, 4><<<grid, block, 0, stream>>>(a, b, d, rows, heads, t); break;
-    case 8: row_dot16_kernel<kFp16, 8><<<grid, block, 0, stream>>>(a, b, d, rows, heads, t); break;
-    case 16: row_dot16_kernel<kFp16, 16><<<grid, block, 0, stream>>>(a, b, d, rows, heads, t); break;
-    default: row_dot16_kernel<kFp16, 32><<<grid, block, 0, stream>>>(a, b, d, rows, heads, t); break;
+    case 1: row_dot16_kernel<kFp16, 1><<<grid, block, 0, stream>>>(a, b, d, rows, pieces, heads, t); break;
+    case 2: row_dot16_kernel<kFp16, 2><<<grid, block, 0, stream>>>(a, b, d, rows, pieces, heads, t); break;
+    case 4: row_dot16_kernel<kFp16, 4><<<grid, block, 0, stream>>>(a, b, d, rows, pieces, heads, t); break;
+    case 8: row_dot16_kernel<kFp16, 8><<<grid, block, 0, stream>>>(a, b, d, rows, pieces, heads, t); break;
+    case 16: row_dot16_kernel<kFp16, 16><<<grid, block, 0, stream>>>(a, b, d, rows, pieces, heads, t); break;
+    default: row_dot16_kernel<kFp16, 32><<<grid, block, 0, stream>>>(a, b, d, rows, pieces, heads, t); break;
   }
   return true;
 }
@@ -459,7 +464,7 @@ int general_delta_bthd(const void* out, const void* dout, void* delta, int dtype
     note_launches(1);
     return LIMN_B200_OK;
   }
-  return fail(LIMN_B200_UNSUPPORTED, "sdpa_delta: the (batch, t, heads, hd) layout is served for f16/bf16 with hd_v a power of two from 8 to 256");
+  return fail(LIMN_B200_UNSUPPORTED, "sdpa_delta: the (batch, t, heads, hd) layout is served for f16/bf16 with hd_v a multiple of 8 up to 256");
 }
 
 }  // namespace limn_b200

@@ -139,7 +139,7 @@ def read_views_in_place() -> Callable[[], None]:
             return plain()
         batch, heads, t_q, hd = q.shape
         t_k = k.shape[2]
-        if k.shape != (batch, heads, t_k, hd) or v.shape != (batch, heads, t_k, hd) or hd not in (64, 128) or (causal and t_q != t_k):
+        if k.shape != (batch, heads, t_k, hd) or v.shape != (batch, heads, t_k, hd) or hd % 8 or hd > 128 or (causal and t_q != t_k):
             return plain()
         found = [under(t) for t in (q, k, v)]
         if any(f is None for f in found):

@@ -23,6 +23,8 @@ CASES = [
     (1, 5, 257, 257, 128, True, BF16),
     (2, 2, 130, 390, 128, False, np.dtype(np.float16)),
     (3, 4, 128, 128, 64, False, BF16),
+    (2, 3, 200, 200, 96, True, BF16),  # narrower heads run zero-padded in the 128 and the 64 kernel
+    (2, 2, 150, 150, 40, False, np.dtype(np.float16)),
 ]
 
 
@@ -100,7 +102,7 @@ def test_token_major_with_a_key_mask_matches_the_oracle():
     assert (widen(got["dk"].transpose(0, 2, 1, 3))[:, :, 150:] == 0).all()
 
 
-@pytest.mark.parametrize("hd,causal,t", [(64, True, 300), (128, False, 257)], ids=["d64 causal", "d128 full"])
+@pytest.mark.parametrize("hd,causal,t", [(64, True, 300), (128, False, 257), (80, True, 200)], ids=["d64 causal", "d128 full", "d80 causal"])
 def test_slices_of_one_projection_buffer_give_the_dense_bits(hd, causal, t):
     """The strided entry points on what a transformer layer really holds: q, k, v as slices of one
     (batch, t, 3, heads, hd) projection output, dO and the results token-major, dK and dV written straight into a

@@ -71,7 +71,11 @@ ORACLE_CASES = [
     ("f16 d128 full 200", np.float16, (2, 200, 128), (2, 200, 128), (2, 200, 128), False, 1.0, False),
     ("f32 d64 causal 300", np.float32, (2, 300, 64), (2, 300, 64), (2, 300, 64), True, 1.0, False),
     ("f32 d128 full 130", np.float32, (130, 128), (130, 128), (130, 128), False, 1.0, False),
-    ("bf16 d32 causal (general path)", BF16, (2, 2, 200, 32), (2, 2, 200, 32), (2, 2, 200, 32), True, 1.0, False),
+    ("bf16 d32 causal (zero-padded in the 64 kernel)", BF16, (2, 2, 200, 32), (2, 2, 200, 32), (2, 2, 200, 32), True, 1.0, False),
+    ("bf16 d96 full 300 (zero-padded in the 128 kernel)", BF16, (3, 300, 96), (3, 300, 96), (3, 300, 96), False, 1.0, False),
+    ("f16 d80 causal 257", np.float16, (2, 257, 80), (2, 257, 80), (2, 257, 80), True, 1.0, False),
+    ("bf16 d8 causal 130", BF16, (2, 130, 8), (2, 130, 8), (2, 130, 8), True, 1.0, False),
+    ("bf16 d20 causal (general path)", BF16, (2, 2, 200, 20), (2, 2, 200, 20), (2, 2, 200, 20), True, 1.0, False),
     ("bf16 hd 64 hd_v 128 (general path)", BF16, (2, 150, 64), (2, 150, 64), (2, 150, 128), False, 1.0, False),
     ("f64 d40", np.float64, (2, 70, 40), (2, 70, 40), (2, 70, 24), True, 1.0, False),
 ]
@@ -125,6 +129,7 @@ MASK_CASES = [
     ("d128 causal, padded batch", (3, 384, 128), True, "pad"),
     ("d128 full, padded batch, ragged", (2, 200, 128), False, "pad"),
     ("d64 causal, keys hidden at random", (2, 2, 257, 64), True, "holes"),
+    ("d96 causal, keys hidden at random (zero-padded head)", (2, 2, 257, 96), True, "holes"),
 ]
 
 
@@ -187,8 +192,8 @@ TILED_CASES = [
     ("f32 d64 causal, keys hidden at random", np.float32, (2, 2, 257, 64), (2, 2, 257, 64), (2, 2, 257, 64), True, "holes"),
     ("f32 d128 full, padded batch", np.float32, (3, 200, 128), (3, 200, 128), (3, 200, 128), False, "pad"),
     ("f32 d32 rect 16x16 (the smallest tiled sides)", np.float32, (5, 16, 32), (5, 16, 32), (5, 16, 32), False, None),
-    ("f16 d96 causal 300", np.float16, (2, 300, 96), (2, 300, 96), (2, 300, 96), True, None),
-    ("bf16 d32 full 500, padded batch", BF16, (2, 500, 32), (2, 500, 32), (2, 500, 32), False, "pad"),
+    ("f16 d100 causal 300", np.float16, (2, 300, 100), (2, 300, 100), (2, 300, 100), True, None),
+    ("bf16 d36 full 500, padded batch", BF16, (2, 500, 36), (2, 500, 36), (2, 500, 36), False, "pad"),
     ("bf16 hd 128 hd_v 64 rect 100x260", BF16, (2, 100, 128), (2, 260, 128), (2, 260, 64), False, None),
 ]
 
@@ -261,6 +266,8 @@ FUSED_CASES = [
     ("bf16 d64 full ragged", BF16, 2, (2, 200, 64), False, False, "bhtd"),
     ("f16 d64 causal masked", np.float16, 1, (4, 300, 64), True, True, "bhtd"),
     ("bf16 d128 full token-major", BF16, 2, (6, 260, 128), False, False, "bthd"),
+    ("bf16 d96 causal (zero-padded head)", BF16, 2, (3, 300, 96), True, False, "bhtd"),
+    ("f16 d40 full token-major (zero-padded head)", np.float16, 1, (4, 200, 40), False, False, "bthd"),
     ("f32 d32 causal (general path)", np.float32, 0, (2, 100, 32), True, False, "bhtd"),
 ]
 
