@@ -1074,6 +1074,33 @@ def profile_decode(args) -> None:
     print(json.dumps({"profiled": "decode one_row_4096_keys_d128", "problems": bh, "device_status": runtime.device_status()}))
 
 
+def profile_float32(args) -> None:
+    """For profiler captures: the float32 case B=4 H=16 S=1024 D=128 causal of `others.float32` (forward, row dot, dQ,
+    dK/dV on the tiled CUDA-core kernels), launched `--steps` times after one warm-up pass."""
+    import torch
+
+    from limn_b200 import runtime
+    from limn_b200._lib import lib
+
+    torch.cuda.set_device(0)
+    runtime.set_device(0)
+    L = lib()
+    bh, s, d = 64, 1024, 128
+    q, k, v, do = (torch.randn((bh, s, d), device="cuda") for _ in range(4))
+    out, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
+    lse, delta = (torch.empty((bh, s), dtype=torch.float32, device="cuda") for _ in range(2))
+    tail = (0, bh, s, s, d, d, 1, d ** -0.5, None)
+    for _ in range(1 + args.steps):
+        codes = (L.limn_b200_sdpa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), None, out.data_ptr(), lse.data_ptr(), *tail),
+                 L.limn_b200_sdpa_delta(out.data_ptr(), do.data_ptr(), delta.data_ptr(), 0, bh * s, d, None),
+                 L.limn_b200_sdpa_bwd_q(q.data_ptr(), k.data_ptr(), v.data_ptr(), do.data_ptr(), lse.data_ptr(), delta.data_ptr(), None, dq.data_ptr(), *tail),
+                 L.limn_b200_sdpa_bwd_kv(q.data_ptr(), k.data_ptr(), v.data_ptr(), do.data_ptr(), lse.data_ptr(), delta.data_ptr(), None, dk.data_ptr(), dv.data_ptr(), *tail))
+        if any(codes):
+            raise SystemExit(L.limn_b200_last_error().decode())
+    torch.cuda.synchronize()
+    print(json.dumps({"profiled": "float32 B4_H16_S1024_D128_causal", "problems": bh, "device_status": runtime.device_status()}))
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -1083,6 +1110,7 @@ def main() -> None:
     parser.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT_WORKLOAD)
     parser.add_argument("--profile", type=int, default=0, metavar="N", help="launch the kernels over the first N problems and exit (for ncu)")
     parser.add_argument("--profile-decode", action="store_true", help="launch the decode case of others.decode and exit (for ncu)")
+    parser.add_argument("--profile-float32", action="store_true", help="launch a float32 case of others.float32 and exit (for ncu)")
     parser.add_argument("--backward", action="store_true", help="with --profile: run the backward kernels even for a forward-only workload")
     parser.add_argument("--no-others", dest="others", action="store_false", help="time only the named workload")
     parser.add_argument("--rest-seconds", type=float, default=0.5, help="pause before each burst trial")
@@ -1094,6 +1122,8 @@ def main() -> None:
         limn_arm(args.limn_arm)
     elif args.profile_decode:
         profile_decode(args)
+    elif args.profile_float32:
+        profile_float32(args)
     elif args.profile:
         profile_case(args)
     elif args.impl == "reference":
