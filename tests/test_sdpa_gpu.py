@@ -75,6 +75,7 @@ ORACLE_CASES = [
     ("bf16 d96 full 300 (zero-padded in the 128 kernel)", BF16, (3, 300, 96), (3, 300, 96), (3, 300, 96), False, 1.0, False),
     ("f16 d80 causal 257", np.float16, (2, 257, 80), (2, 257, 80), (2, 257, 80), True, 1.0, False),
     ("bf16 d8 causal 130", BF16, (2, 130, 8), (2, 130, 8), (2, 130, 8), True, 1.0, False),
+    ("bf16 d96 one row against 300 keys", BF16, (2, 1, 96), (2, 300, 96), (2, 300, 96), False, 1.0, False),
     ("bf16 d20 causal (general path)", BF16, (2, 2, 200, 20), (2, 2, 200, 20), (2, 2, 200, 20), True, 1.0, False),
     ("bf16 hd 64 hd_v 128 (general path)", BF16, (2, 150, 64), (2, 150, 64), (2, 150, 128), False, 1.0, False),
     ("f64 d40", np.float64, (2, 70, 40), (2, 70, 40), (2, 70, 24), True, 1.0, False),
