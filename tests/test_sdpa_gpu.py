@@ -124,6 +124,31 @@ def test_every_tail_length_d64_bf16(t, dev):
         close(dv, want_dv, 2e-2, f"t={t} dV")
 
 
+@pytest.mark.parametrize("hd", list(range(8, 129, 8)))
+def test_every_head_dim_that_is_a_multiple_of_8(hd, dev):
+    """bf16 heads of 8, 16, ..., 128 columns through the tensor-core kernels (built for 64 and 128; the others run
+    zero-padded in the next of the two): forward and both backward kernels against the oracle, causal, a ragged
+    length, with the operands of the neighbouring problem lying right behind every row's last column."""
+    import limn_standin as host
+    from limn_b200._lib import PATH_TCGEN05, lib
+
+    t = 150
+    assert lib().limn_b200_sdpa_path(2, 3, t, t, hd, hd, 1, 0, hd**-0.5) == PATH_TCGEN05
+    q, k, v, do = _random_case(500 + hd, BF16, (3, t, hd), (3, t, hd), (3, t, hd))
+    scale = hd**-0.5
+    att = host.Attention(dev, q, k, v, causal=True)
+    out, lse = att.forward()
+    want_out, want_lse = oracle.sdpa_forward(q, k, v, causal=True, scale=scale)
+    close(out, want_out, 2e-2, f"hd={hd} O")
+    close(lse, want_lse, LSE_TOL, f"hd={hd} L")
+    dq, dk, dv = att.backward(do)
+    delta = oracle.row_delta(do, want_out)
+    close(dq, oracle.sdpa_backward_q(q, k, v, do, want_lse, delta, causal=True, scale=scale), 2e-2, f"hd={hd} dQ")
+    want_dk, want_dv = oracle.sdpa_backward_kv(q, k, v, do, want_lse, delta, causal=True, scale=scale)
+    close(dk, want_dk, 2e-2, f"hd={hd} dK")
+    close(dv, want_dv, 2e-2, f"hd={hd} dV")
+
+
 MASK_CASES = [
     # id, shape (q = k = v), causal, mask kind
     ("d64 full, keys hidden at random", (2, 3, 300, 64), False, "holes"),
