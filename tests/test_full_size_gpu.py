@@ -143,3 +143,78 @@ def test_full_size_runs_are_bit_identical():
     second = FullRun("ragged_3000").results
     for key in ("out", "lse", "dq", "dk", "dv"):
         np.testing.assert_array_equal(first[key].view(np.uint8), second[key].view(np.uint8))
+
+
+def test_operands_past_2_31_elements():
+    """The largest case: 520 problems of 32 768 tokens at head dim 128, 2.18e9 elements (4.4 GB) per operand, so that
+    element offsets no longer fit 32 bits and a problem's tiles lie 8 MB apart. Q, K and dO repeat a seeded block of 8
+    problems; V is that block times a per-problem constant, so a problem that read its neighbour's tiles would show.
+    Rows of O, L, dQ, dK and dV sampled over the batch (its first and last problems and the three around the 2^31st
+    element) are compared with a row-wise numpy evaluation of limn/sdpa.py:114-203, which needs one row's scores at a
+    time instead of the 4 GB score matrix of a problem."""
+    torch = pytest.importorskip("torch")
+    from limn_b200 import runtime
+    from limn_b200._lib import check, lib
+
+    L = lib()
+    block, bh, s, d = 8, 520, 32768, 128
+    assert bh * s * d > 2**31
+    scale = d**-0.5
+    rng = np.random.default_rng(2031)
+    base = [(rng.standard_normal((block, s, d), dtype=np.float32) * m).astype(BF16) for m in (0.5, 0.5, 1.0, 1.0)]
+    consts = 0.25 * (1 + np.arange(bh) % 7)
+    dev = torch.device("cuda", 0)
+    runtime.set_device(0)
+    on_device = [torch.from_numpy(a.view(np.int16)).to(dev).view(torch.bfloat16) for a in base]
+    q, k, vb, do = (t.repeat(bh // block, 1, 1) for t in on_device)
+    v = (vb.float() * torch.from_numpy(consts.astype(np.float32)).to(dev)[:, None, None]).to(torch.bfloat16)
+    del vb
+    out, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
+    lse, delta = (torch.empty((bh, s), dtype=torch.float32, device=dev) for _ in range(2))
+    tail = (2, bh, s, s, d, d, 1, scale, None)
+    check(L.limn_b200_sdpa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), None, out.data_ptr(), lse.data_ptr(), *tail), "sdpa")
+    check(L.limn_b200_sdpa_bwd_q_fused(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), do.data_ptr(), lse.data_ptr(), None,
+                                       dq.data_ptr(), delta.data_ptr(), *tail), "sdpa_bwd_q")
+    check(L.limn_b200_sdpa_bwd_kv(q.data_ptr(), k.data_ptr(), v.data_ptr(), do.data_ptr(), lse.data_ptr(), delta.data_ptr(), None,
+                                  dk.data_ptr(), dv.data_ptr(), *tail), "sdpa_bwd_kv")
+    torch.cuda.synchronize()
+    assert runtime.device_status() == 0
+
+    f32 = lambda a: a.astype(np.float32)
+    host = lambda t, p, rows: t[p, rows].float().cpu().numpy()
+    edge = -(-(2**31) // (s * d))  # the first problem that starts past the 2^31st element
+    for p in (0, 1, edge - 1, edge, edge + 1, bh - 1):
+        qb, kb, dob = (f32(a[p % block]) for a in (base[0], base[1], base[3]))
+        vp = f32((f32(base[2][p % block]) * np.float32(consts[p])).astype(BF16))  # V as the device holds it
+        rows = [0, 1, 127, 128, 4095, 20000, s - 1]
+        want_o, want_l, want_dq = [], [], []
+        for i in rows:
+            sc = (kb[: i + 1] @ qb[i]) * scale
+            top = sc.max()
+            w = np.exp(sc - top)
+            den = w.sum()
+            o = (w @ vp[: i + 1]) / den
+            want_o.append(o)
+            want_l.append(top + np.log(den))
+            dp = vp[: i + 1] @ dob[i]
+            ds = (w / den) * (dp - dob[i] @ o) * scale
+            want_dq.append(ds @ kb[: i + 1])
+        parity(host(out, p, rows), np.array(want_o, np.float32), 2e-2, f"problem {p} O")
+        parity(host(lse, p, rows), np.array(want_l, np.float32), 1e-3, f"problem {p} L")
+        parity(host(dq, p, rows), np.array(want_dq, np.float32), 2e-2, f"problem {p} dQ")
+        # dK and dV of late keys: only the last queries see them, and the device's L and delta for those rows are
+        # what the kernels read (L was checked above on a sample of the same rows' neighbours)
+        first = s - 300
+        li = lse[p, first:].cpu().numpy()
+        di = delta[p, first:].cpu().numpy()
+        keys = [first, s - 129, s - 128, s - 1]
+        want_dk, want_dv = [], []
+        for j in keys:
+            i0 = j - first
+            sc = (qb[j:] @ kb[j]) * scale
+            pj = np.exp(sc - li[i0:])
+            want_dv.append(pj @ dob[j:])
+            dpj = dob[j:] @ vp[j]
+            want_dk.append((pj * (dpj - di[i0:]) * scale) @ qb[j:])
+        parity(host(dk, p, keys), np.array(want_dk, np.float32), 2e-2, f"problem {p} dK")
+        parity(host(dv, p, keys), np.array(want_dv, np.float32), 2e-2, f"problem {p} dV")
