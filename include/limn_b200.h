@@ -40,7 +40,7 @@ enum limn_b200_status {
 /* Which kernel family served (or would serve) a problem. */
 enum limn_b200_path {
   LIMN_B200_PATH_GENERAL = 0,  /* SIMT kernels: any float dtype, any hd/hd_v */
-  LIMN_B200_PATH_TCGEN05 = 1,  /* TMA + tcgen05 kernels: f16/bf16, hd == hd_v a multiple of 8 up to 128 (run as 64 or 128), any t_q/t_k, with or without key mask */
+  LIMN_B200_PATH_TCGEN05 = 1,  /* TMA + tcgen05 kernels: f16/bf16, hd and hd_v multiples of 8 up to 128 (run as 64 or 128), any t_q/t_k, with or without key mask */
   LIMN_B200_PATH_DECODE = 2    /* forward only: f16/bf16, hd == hd_v in {64, 128}, t_q <= 4 without a causal mask (the step of a
                                   kv cache): one CTA streams a problem's keys and values once, bound by HBM, no tensor cores */
 };
@@ -119,7 +119,7 @@ int limn_b200_sdpa_delta(const void* out, const void* dout, void* delta,
  *     points above with bh = batch * heads.
  *   layout LIMN_B200_BTHD: they are (batch, t, heads, hd) dense.
  *   Either way lse and delta are (batch * heads, t_q) and key_mask (batch * heads, t_k), as above.
- *   LIMN_B200_BTHD is served for f16/bf16 with hd == hd_v a multiple of 8 up to 128 (the tensor-core kernels); anything else
+ *   LIMN_B200_BTHD is served for f16/bf16 with hd and hd_v multiples of 8 up to 128 (the tensor-core kernels); anything else
  *   returns LIMN_B200_UNSUPPORTED and launches nothing. */
 enum limn_b200_layout {
   LIMN_B200_BHTD = 0,
@@ -153,8 +153,8 @@ int limn_b200_sdpa_delta_layout(const void* out, const void* dout, void* delta,
  * (batch, head, row) stride triple per operand, in elements (columns are contiguous; every stride a multiple of 8,
  * every pointer 16-byte aligned and already offset to the operand's first element), so a frontend can hand over its
  * views as they are instead of copying them (limn/tensor.py:561-562, :736-746 make those copies). lse and delta stay
- * (batch * heads, t_q), key_mask (batch * heads, t_k). No counterpart in the reference. f16/bf16 with hd == hd_v a
- * multiple of 8 up to 128 only; anything else returns LIMN_B200_UNSUPPORTED and launches nothing.
+ * (batch * heads, t_q), key_mask (batch * heads, t_k). No counterpart in the reference. f16/bf16 with hd and hd_v
+ * multiples of 8 up to 128 only; anything else returns LIMN_B200_UNSUPPORTED and launches nothing.
  *   limn_b200_sdpa_fwd_strided:          strides of q, k, v, out                 (4 triples)
  *   limn_b200_sdpa_bwd_q_fused_strided:  strides of q, k, v, out, dout, dq        (6 triples); delta is written
  *   limn_b200_sdpa_bwd_kv_strided:       strides of q, k, v, dout, dk, dv         (6 triples) */

@@ -204,7 +204,7 @@ int validate_op(Op op, const char* name, const Problem& p) {
   if (!have_inputs || !have_rest) return fail(LIMN_B200_BAD_ARGUMENT, "%s: a required pointer is null", name);
   if (p.bh > 0 && !tcgen05_serves(op, p) && p.layout != LIMN_B200_BHTD)
     return fail(LIMN_B200_UNSUPPORTED,
-                "%s: the (batch, t, heads, hd) layout is served for f16/bf16 with hd == hd_v a multiple of 8 up to 128; make the "
+                "%s: the (batch, t, heads, hd) layout is served for f16/bf16 with hd and hd_v multiples of 8 up to 128; make the "
                 "operands contiguous as (batch, heads, t, hd) for anything else",
                 name);
   return LIMN_B200_OK;
@@ -344,7 +344,7 @@ int with_strides(const char* name, Problem& p, int batch, int heads, const long 
 int strided_dispatch(Op op, const char* name, const Problem& p) {
   if (int rc = validate_op(op, name, p)) return rc;
   if (p.bh > 0 && !tcgen05_serves(op, p))
-    return fail(LIMN_B200_UNSUPPORTED, "%s: strided operands are served for f16/bf16 with hd == hd_v a multiple of 8 up to 128; make the operands contiguous for anything else", name);
+    return fail(LIMN_B200_UNSUPPORTED, "%s: strided operands are served for f16/bf16 with hd and hd_v multiples of 8 up to 128; make the operands contiguous for anything else", name);
   return dispatch_op(op, name, p);
 }
 

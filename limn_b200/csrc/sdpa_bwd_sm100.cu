@@ -1,4 +1,4 @@
-// "sdpa_bwd_q" and "sdpa_bwd_kv" for f16/bf16 with hd == hd_v a multiple of 8 up to 128 (kernels for 64 and 128; a
+// "sdpa_bwd_q" and "sdpa_bwd_kv" for f16/bf16 with hd and hd_v multiples of 8 up to 128 (kernels for 64 and 128; a
 // narrower head runs in the next of the two, its missing columns read as zeros by TMA and never stored): TMA-staged
 // tiles, tcgen05 MMAs accumulating in tensor memory, probabilities rebuilt from the saved
 // log-sum-exp. Two separate passes, as in the kernels these replace (limn/cuda_emit.py:968-1083):
@@ -138,7 +138,8 @@ struct BwdParams {
   Strides o_strides, do_strides;  // fused dQ pass: of the rows of O and dO the row statistic is computed from
   unsigned items;      // work items: bh * (tiles of 128 rows a problem's owner side has)
   int t_q, t_k;
-  int width;           // head dim of the operands as they lie in memory (<= D): TMA zero-fills the rest, stores skip it
+  int width;           // columns of Q, K, dQ, dK as they lie in memory (<= D): TMA zero-fills the rest, stores skip it
+  int width_v;         // the same of V, dO, O, dV
   int q_tiles, kv_tiles;
   float scale;
 };
@@ -808,7 +809,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           uint32_t acc[32];
           tmem_ld32(t_acc + 32 * c, acc);
           tmem_ld_wait();
-          if (in) store_row32<kFp16>(dst, out_at + 32 * c, acc, mul, prm.width - 32 * c);
+          if (in) store_row32<kFp16>(dst, out_at + 32 * c, acc, mul, (group == 0 ? prm.width_v : prm.width) - 32 * c);
         }
       } else {
         // each group writes half of this query's dQ row
@@ -855,7 +856,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const int row = min(item.own0 + local, prm.t_q - 1);
         const long long o_at = (item.batch * prm.o_strides.batch + item.head * prm.o_strides.head + row * prm.o_strides.row) * 2;
         const long long do_at = (item.batch * prm.do_strides.batch + item.head * prm.do_strides.head + row * prm.do_strides.row) * 2;
-        const float d = row_dot<D, kFp16>(static_cast<const unsigned char*>(prm.o_rows) + o_at, static_cast<const unsigned char*>(prm.do_rows) + do_at, prm.width >> 3);
+        const float d = row_dot<D, kFp16>(static_cast<const unsigned char*>(prm.o_rows) + o_at, static_cast<const unsigned char*>(prm.do_rows) + do_at, prm.width_v >> 3);
         delta_ring[slot][local] = d;
         if (item.own0 + local < prm.t_q) prm.delta_out[static_cast<long long>(item.problem) * prm.t_q + row] = d;
       }
@@ -890,8 +891,8 @@ int launch_bwd(const Problem& p) {
   const int heads = p.heads > 0 ? p.heads : static_cast<int>(p.bh), batch = static_cast<int>(p.bh / heads);
   if (int rc = make_tile_map(&map_q, p.q, kFp16, batch, heads, p.t_q, p.hd, kTile, operand_strides(p, kOpQ, heads, p.t_q, p.hd))) return rc;
   if (int rc = make_tile_map(&map_k, p.k, kFp16, batch, heads, p.t_k, p.hd, kTile, operand_strides(p, kOpK, heads, p.t_k, p.hd))) return rc;
-  if (int rc = make_tile_map(&map_v, p.v, kFp16, batch, heads, p.t_k, p.hd, kTile, operand_strides(p, kOpV, heads, p.t_k, p.hd))) return rc;
-  if (int rc = make_tile_map(&map_do, p.dout, kFp16, batch, heads, p.t_q, p.hd, kTile, operand_strides(p, kOpDout, heads, p.t_q, p.hd))) return rc;
+  if (int rc = make_tile_map(&map_v, p.v, kFp16, batch, heads, p.t_k, p.hd_v, kTile, operand_strides(p, kOpV, heads, p.t_k, p.hd_v))) return rc;
+  if (int rc = make_tile_map(&map_do, p.dout, kFp16, batch, heads, p.t_q, p.hd_v, kTile, operand_strides(p, kOpDout, heads, p.t_q, p.hd_v))) return rc;
   BwdParams prm;
   prm.mask = static_cast<const unsigned short*>(p.mask);
   prm.lse = static_cast<const float*>(p.lse_in);
@@ -903,9 +904,9 @@ int launch_bwd(const Problem& p) {
   prm.out1 = kKV ? p.dv : nullptr;
   prm.heads = heads;
   prm.out_strides = kKV ? operand_strides(p, kOpDk, heads, p.t_k, p.hd) : operand_strides(p, kOpDq, heads, p.t_q, p.hd);
-  prm.out1_strides = operand_strides(p, kOpDv, heads, p.t_k, p.hd);
-  prm.o_strides = operand_strides(p, kOpOut, heads, p.t_q, p.hd);
-  prm.do_strides = operand_strides(p, kOpDout, heads, p.t_q, p.hd);
+  prm.out1_strides = operand_strides(p, kOpDv, heads, p.t_k, p.hd_v);
+  prm.o_strides = operand_strides(p, kOpOut, heads, p.t_q, p.hd_v);
+  prm.do_strides = operand_strides(p, kOpDout, heads, p.t_q, p.hd_v);
   {
     const long long all = prm.out_strides.batch | prm.out_strides.head | prm.out_strides.row | prm.out1_strides.batch |
                           prm.out1_strides.head | prm.out1_strides.row | prm.o_strides.batch | prm.o_strides.head | prm.o_strides.row;
@@ -919,6 +920,7 @@ int launch_bwd(const Problem& p) {
   prm.bh = p.bh;
   prm.t_q = p.t_q, prm.t_k = p.t_k;
   prm.width = p.hd;
+  prm.width_v = p.hd_v;
   prm.q_tiles = (p.t_q + kTile - 1) / kTile;
   prm.kv_tiles = (p.t_k + kTile - 1) / kTile;
 #ifdef LIMN_TRACE
@@ -967,7 +969,7 @@ int launch_bwd_d(const Problem& p) {
 
 }  // namespace
 
-int tcgen05_bwd_q(const Problem& p) { return p.hd > 64 ? launch_bwd_d<128, false>(p) : launch_bwd_d<64, false>(p); }
-int tcgen05_bwd_kv(const Problem& p) { return p.hd > 64 ? launch_bwd_d<128, true>(p) : launch_bwd_d<64, true>(p); }
+int tcgen05_bwd_q(const Problem& p) { return (p.hd > 64 || p.hd_v > 64) ? launch_bwd_d<128, false>(p) : launch_bwd_d<64, false>(p); }
+int tcgen05_bwd_kv(const Problem& p) { return (p.hd > 64 || p.hd_v > 64) ? launch_bwd_d<128, true>(p) : launch_bwd_d<64, true>(p); }
 
 }  // namespace limn_b200

@@ -1,7 +1,8 @@
-// "sdpa" forward for f16/bf16 with hd == hd_v a multiple of 8 up to 128, with or without a key mask: TMA-staged tiles,
+// "sdpa" forward for f16/bf16 with hd and hd_v multiples of 8 up to 128, with or without a key mask: TMA-staged tiles,
 // tcgen05 MMAs accumulating in tensor memory, online softmax with one thread per query row. The kernels are built for
 // head dims 64 and 128; a narrower head runs in the next of the two: TMA fills the columns a row does not have with
-// zeros, which add nothing to a score and give zero output columns that are not stored.
+// zeros, which add nothing to a score and give zero output columns that are not stored. hd and hd_v may differ for
+// the same reason: Q and K are read with hd columns, V with hd_v, and O is stored hd_v wide.
 //
 // A work item is two consecutive tiles of 128 query rows of one (batch, head) problem; the problem's keys
 // and values stream past them in tiles of 128 keys:
@@ -120,7 +121,7 @@ struct FwdParams {
   Strides out_strides; // of O, in elements
   unsigned items;      // work items: bh * q_pairs
   int t_q, t_k;
-  int width;        // head dim of the operands as they lie in memory (<= D)
+  int width;        // columns of V and O as they lie in memory (<= D)
   int q_pairs;      // work items per problem
   int kv_tiles;     // ceil(t_k / 128)
   float scale;
@@ -589,12 +590,12 @@ int launch_fwd(const Problem& p) {
   const int heads = p.heads > 0 ? p.heads : static_cast<int>(p.bh), batch = static_cast<int>(p.bh / heads);
   if (int rc = make_tile_map(&map_q, p.q, kFp16, batch, heads, p.t_q, p.hd, kTileRows, operand_strides(p, kOpQ, heads, p.t_q, p.hd))) return rc;
   if (int rc = make_tile_map(&map_k, p.k, kFp16, batch, heads, p.t_k, p.hd, kTileRows, operand_strides(p, kOpK, heads, p.t_k, p.hd))) return rc;
-  if (int rc = make_tile_map(&map_v, p.v, kFp16, batch, heads, p.t_k, p.hd, kTileRows, operand_strides(p, kOpV, heads, p.t_k, p.hd))) return rc;
+  if (int rc = make_tile_map(&map_v, p.v, kFp16, batch, heads, p.t_k, p.hd_v, kTileRows, operand_strides(p, kOpV, heads, p.t_k, p.hd_v))) return rc;
   FwdParams prm;
   prm.out = p.out;
   prm.heads = heads;
-  prm.out_strides = operand_strides(p, kOpOut, heads, p.t_q, p.hd);
-  prm.width = p.hd;
+  prm.out_strides = operand_strides(p, kOpOut, heads, p.t_q, p.hd_v);
+  prm.width = p.hd_v;
   if ((prm.out_strides.batch | prm.out_strides.head | prm.out_strides.row) & 7)
     return fail(LIMN_B200_BAD_ARGUMENT, "sdpa: operand strides must be multiples of 8 elements");
   if (reinterpret_cast<uintptr_t>(p.out) & 15u) return fail(LIMN_B200_BAD_ARGUMENT, "sdpa: the output is not 16-byte aligned");
@@ -651,6 +652,6 @@ int launch_fwd_d(const Problem& p) {
 
 }  // namespace
 
-int tcgen05_fwd(const Problem& p) { return p.hd > 64 ? launch_fwd_d<128>(p) : launch_fwd_d<64>(p); }
+int tcgen05_fwd(const Problem& p) { return (p.hd > 64 || p.hd_v > 64) ? launch_fwd_d<128>(p) : launch_fwd_d<64>(p); }
 
 }  // namespace limn_b200

@@ -98,12 +98,13 @@ def test_dispatch_policy():
     assert path(2, 2, 64, 64, 64, 64, 0, 1, 0.125) == PATH_TCGEN05  # key mask, 16-bit storage
     assert path(2, 2, 64, 64, 32, 32, 1, 0, 0.2) == PATH_TCGEN05  # a narrower head runs zero-padded in the 64 kernel
     assert path(1, 2, 64, 64, 96, 96, 0, 0, 0.1) == PATH_TCGEN05  # or in the 128 kernel
+    assert path(2, 2, 64, 64, 64, 128, 0, 0, 0.125) == PATH_TCGEN05  # hd != hd_v: each operand at its own width
     for general in (
         (0, 2, 128, 128, 32, 32, 1, 0, 32**-0.5),  # float32 computes at its own width
         (3, 2, 64, 64, 64, 64, 1, 0, 0.125),  # float64
         (2, 2, 64, 64, 36, 36, 1, 0, 0.2),  # a head dim that is no multiple of 8
         (2, 2, 64, 64, 136, 136, 1, 0, 0.2),  # or above 128
-        (2, 2, 64, 64, 64, 128, 0, 0, 0.125),  # hd != hd_v
+        (2, 2, 64, 64, 64, 132, 0, 0, 0.125),  # hd_v no multiple of 8
         (2, 2, 64, 64, 64, 64, 0, 0, -0.125),  # non-positive scale
     ):
         assert path(*general) == PATH_GENERAL

@@ -77,7 +77,9 @@ ORACLE_CASES = [
     ("bf16 d8 causal 130", BF16, (2, 130, 8), (2, 130, 8), (2, 130, 8), True, 1.0, False),
     ("bf16 d96 one row against 300 keys", BF16, (2, 1, 96), (2, 300, 96), (2, 300, 96), False, 1.0, False),
     ("bf16 d20 causal (general path)", BF16, (2, 2, 200, 20), (2, 2, 200, 20), (2, 2, 200, 20), True, 1.0, False),
-    ("bf16 hd 64 hd_v 128 (general path)", BF16, (2, 150, 64), (2, 150, 64), (2, 150, 128), False, 1.0, False),
+    ("bf16 hd 64 hd_v 128 (both in the 128 kernel)", BF16, (2, 150, 64), (2, 150, 64), (2, 150, 128), False, 1.0, False),
+    ("bf16 hd 128 hd_v 64 rect 100x260", BF16, (2, 100, 128), (2, 260, 128), (2, 260, 64), False, 1.0, False),
+    ("f16 hd 48 hd_v 24 causal 200", np.float16, (3, 200, 48), (3, 200, 48), (3, 200, 24), True, 1.0, False),
     ("f64 d40", np.float64, (2, 70, 40), (2, 70, 40), (2, 70, 24), True, 1.0, False),
 ]
 
@@ -220,7 +222,7 @@ TILED_CASES = [
     ("f32 d32 rect 16x16 (the smallest tiled sides)", np.float32, (5, 16, 32), (5, 16, 32), (5, 16, 32), False, None),
     ("f16 d100 causal 300", np.float16, (2, 300, 100), (2, 300, 100), (2, 300, 100), True, None),
     ("bf16 d36 full 500, padded batch", BF16, (2, 500, 36), (2, 500, 36), (2, 500, 36), False, "pad"),
-    ("bf16 hd 128 hd_v 64 rect 100x260", BF16, (2, 100, 128), (2, 260, 128), (2, 260, 64), False, None),
+    ("bf16 hd 100 hd_v 60 rect 100x260", BF16, (2, 100, 100), (2, 260, 100), (2, 260, 60), False, None),
 ]
 
 
