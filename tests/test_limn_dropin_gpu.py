@@ -281,7 +281,8 @@ def test_the_frontend_patch_for_the_fused_row_dot(limn):
             np.testing.assert_allclose(g, w, rtol=3e-2, atol=3e-2)
 
 
-def test_attention_over_views_in_place(limn):
+@pytest.mark.parametrize("hd", [64, 40], ids=["hd 64", "hd 40 (zero-padded in the 64 kernel)"])
+def test_attention_over_views_in_place(limn, hd):
     """limn_b200.frontend.read_views_in_place(): an attention layer as a model writes it (one projection, q, k, v as
     slices of it, the result permuted back for the output projection) on limn's cuda device: the gradient with
     respect to the projection matches limn's numpy device, the plan has no copy kernel per operand any more, and the
@@ -289,7 +290,7 @@ def test_attention_over_views_in_place(limn):
     import limn_b200
     from limn_b200 import frontend as patch
 
-    b, t, heads, hd = 2, 200, 3, 64
+    b, t, heads = 2, 200, 3
     data = rng.standard_normal((b, t, 3 * heads * hd)).astype(np.float32)
     weight = rng.standard_normal((b, t, heads * hd)).astype(np.float32)
 
