@@ -119,7 +119,7 @@ cudaError_t launch_overlapped(void (*kernel)(Params...), dim3 grid, dim3 block, 
 
 // Kernel families. Each returns a status code and enqueues on p.stream.
 int general_launch(Op op, const Problem& p);
-// The tiled members of the general family (float32/float16/bfloat16, head dims up to 128, sides of 16 rows and
+// The tiled members of the general family (float32/float16/bfloat16, head dims up to 256, sides of 16 rows and
 // more); general_launch hands them what they serve and keeps the rest for the one-row-per-warp kernels.
 bool general_tiled_serves(Op op, const Problem& p);
 int general_tiled_launch(Op op, const Problem& p);

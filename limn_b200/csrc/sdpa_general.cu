@@ -3,7 +3,7 @@
 // (float32 and float64 in particular, which have to be computed at their own width to meet
 // the reference's 1e-5 / 1e-12 checks: tests/test_attention.py:250-255, limn/sdpa.py:279-291);
 // the tiled kernels of sdpa_general_tiled.cu take over where a problem fills their tiles, and
-// what stays here is float64, head dims above 128 and sides shorter than 16 rows.
+// what stays here is float64, head dims above 256 and sides shorter than 16 rows.
 //
 // Shape of the work: one warp owns one row for the whole pass (a query row in the forward
 // and the dQ pass, a key row in the dK/dV pass), so every total has exactly one owner, no

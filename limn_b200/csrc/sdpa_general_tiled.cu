@@ -1,16 +1,17 @@
 // Tiled SIMT fused-attention kernels: float32, float16 and bfloat16 storage computed in float32 on the
-// CUDA cores, head dims up to 128, optional key mask, rectangular t_q x t_k. They serve what the tcgen05
+// CUDA cores, head dims up to 256, optional key mask, rectangular t_q x t_k. They serve what the tcgen05
 // kernels leave (float32 above all, which has to be computed at its own width to meet the reference's 1e-5
 // check: tests/test_attention.py:250-255) whenever the problem is large enough to fill a tile; the one-row-
 // per-warp kernels in sdpa_general.cu keep float64, wider heads and short sequences.
 //
 // Shape of the work: a block of 256 threads owns 64 rows (query rows in the forward and the dQ pass, key rows
-// in the dK/dV pass) and streams the other side through shared memory in tiles of BN rows. Every tile is two
-// small matrix products on a 16 x 16 thread grid: scores (rows x streamed rows, contraction over the head
-// dim, a 4 x BN/16 micro-tile per thread read from shared memory as float4), then, after the scores went
-// through shared memory, the update of the rows' totals (contraction over the streamed rows, 4 x HD/16 per
-// thread). Each total has one owner and a fixed summation order, no float is added atomically: two runs
-// give the same bits, as the reference's kernels promise (limn/cuda_emit.py:748-752).
+// in the dK/dV pass) and streams the other side through shared memory in tiles of BN rows (64, 32 or 16 of them
+// for head dims up to 64, 128 or 256). Every tile is two small matrix products on a 16 x 16 thread grid: scores
+// (rows x streamed rows, contraction over the head dim, a 4 x BN/16 micro-tile per thread read from shared memory
+// as float4), then, after the scores went through shared memory, the update of the rows' totals (contraction
+// over the streamed rows, 4 x HD/16 per thread). Each total has one owner and a fixed summation order, no float
+// is added atomically: two runs give the same bits, as the reference's kernels promise
+// (limn/cuda_emit.py:748-752).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -457,13 +458,14 @@ int launch_typed(Op op, const Problem& p) {
   const int widest = p.hd > p.hd_v ? p.hd : p.hd_v;
   if (widest <= 32) return launch_sized<T, 32, 64>(op, p);
   if (widest <= 64) return launch_sized<T, 64, 64>(op, p);
-  return launch_sized<T, 128, 32>(op, p);
+  if (widest <= 128) return launch_sized<T, 128, 32>(op, p);
+  return launch_sized<T, 256, 16>(op, p);
 }
 
 }  // namespace
 
 bool general_tiled_serves(Op, const Problem& p) {
-  if (p.dtype == LIMN_B200_F64 || p.hd > 128 || p.hd_v > 128) return false;
+  if (p.dtype == LIMN_B200_F64 || p.hd > 256 || p.hd_v > 256) return false;
   if (p.layout != LIMN_B200_BHTD || p.strided) return false;
   return p.t_q >= 16 && p.t_k >= 16;  // shorter sides leave most of a 64-row tile idle: one row per warp is better
 }

@@ -220,6 +220,8 @@ TILED_CASES = [
     ("f32 d64 causal, keys hidden at random", np.float32, (2, 2, 257, 64), (2, 2, 257, 64), (2, 2, 257, 64), True, "holes"),
     ("f32 d128 full, padded batch", np.float32, (3, 200, 128), (3, 200, 128), (3, 200, 128), False, "pad"),
     ("f32 d32 rect 16x16 (the smallest tiled sides)", np.float32, (5, 16, 32), (5, 16, 32), (5, 16, 32), False, None),
+    ("f32 d256 causal 300", np.float32, (2, 300, 256), (2, 300, 256), (2, 300, 256), True, None),
+    ("bf16 d192 hd_v 128 full 200, keys hidden at random", BF16, (2, 200, 192), (2, 200, 192), (2, 200, 128), False, "holes"),
     ("f16 d100 causal 300", np.float16, (2, 300, 100), (2, 300, 100), (2, 300, 100), True, None),
     ("bf16 d36 full 500, padded batch", BF16, (2, 500, 36), (2, 500, 36), (2, 500, 36), False, "pad"),
     ("bf16 hd 100 hd_v 60 rect 100x260", BF16, (2, 100, 100), (2, 260, 100), (2, 260, 60), False, None),
