@@ -330,7 +330,9 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const unsigned ring = n_item & 1u;
         ok = mbar_wait(bar(B::work_empty + ring), ((n_item >> 1) & 1u) ^ 1u, prm.status, 0x1120u | ring);
         if (!ok) break;
-        const unsigned index = atomicAdd(prm.schedule, 1u);
+        // a CTA's first item is its own number (no round trip to the counter on the way to the first load); the
+        // counter hands out what lies beyond the grid
+        const unsigned index = n_item == 0 ? blockIdx.x : gridDim.x + atomicAdd(prm.schedule, 1u);
         *reinterpret_cast<volatile unsigned*>(&work_ring[ring]) = index;
         mbar_arrive(bar(B::work_full + ring));
         if (index >= prm.items) break;

@@ -225,7 +225,9 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const unsigned slot = n_item & 1u;
         ok = mbar_wait(bar(B::work_empty + slot), ((n_item >> 1) & 1u) ^ 1u, prm.status, 0x0120u | slot);
         if (!ok) break;
-        const unsigned index = atomicAdd(prm.schedule, 1u);
+        // a CTA's first item is its own number (no round trip to the counter on the way to the first load); the
+        // counter hands out what lies beyond the grid
+        const unsigned index = n_item == 0 ? blockIdx.x : gridDim.x + atomicAdd(prm.schedule, 1u);
         *reinterpret_cast<volatile unsigned*>(&work_ring[slot]) = index;
         mbar_arrive(bar(B::work_full + slot));
         if (index >= prm.items) break;
