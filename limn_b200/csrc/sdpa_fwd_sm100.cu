@@ -60,7 +60,7 @@ constexpr int poly_pairs_of_8() {
 #endif
 }
 
-template <int D>
+template <int D, bool kCausal, bool kMask>
 struct FwdLayout {
   static constexpr int kTileBytes = kTileRows * D * 2;
   static constexpr int kAtomBytes = kTileRows * 128;        // one 64-element-wide column block of a tile
@@ -70,9 +70,20 @@ struct FwdLayout {
   static constexpr int kQOff = 0;
   static constexpr int kKOff = kQOff + kQTiles * kTileBytes;
   static constexpr int kVOff = kKOff + kStages * kTileBytes;
-  static constexpr int kBarOff = kVOff + kStages * kTileBytes;
-  static constexpr int kBiasOff = kBarOff + 512;            // room for 64 barriers            // key-mask kernels: [8 warps][2 buffers][128] floats, 0 or -inf per key
-  static constexpr int kBytes = kBiasOff + 8 * 1024 + 1024;  // + slack to align the base to 1024
+  // Where the epilogue leaves O for the tile store: one 64-column block (128 rows x 128 B) per softmax group, which a
+  // group's two blocks take turns in. Used at head dim 128 under a causal mask, where it is worth 2 to 3 %: the two
+  // Q tiles of an item end at different times there and each group's stores are on its own critical path. Without
+  // a causal mask both groups reach the epilogue together and the hand-overs cost more than the stores did (-1 %
+  // at head dim 128, -6 % at 64, measured); with a key mask there is no shared memory left for the block.
+#ifdef LIMN_TILE_STORE_ALL
+  static constexpr bool kTileStore = !(D == 128 && kMask);
+#else
+  static constexpr bool kTileStore = D == 128 && kCausal && !kMask;
+#endif
+  static constexpr int kStageOff = kVOff + kStages * kTileBytes;
+  static constexpr int kBarOff = kStageOff + (kTileStore ? kQTiles * kAtomBytes : 0);
+  static constexpr int kBiasOff = kBarOff + 512;            // room for 64 barriers; then, key-mask kernels only: [8 warps][2 buffers][128] floats, 0 or -inf per key
+  static constexpr int kBytes = kBiasOff + (kMask ? 8 * 1024 : 0) + 1024;  // + slack to align the base to 1024
   // tensor-memory columns
   static constexpr int kSCol = 0;                           // S_t at kSCol + 128 t (P_t overlays its first 64)
   static constexpr int kOCol = 256;                         // O_t at kOCol + D t
@@ -81,7 +92,7 @@ struct FwdLayout {
 // barrier indices inside the barrier block
 template <int D>
 struct FwdBars {
-  static constexpr int kS = FwdLayout<D>::kStages;
+  static constexpr int kS = FwdLayout<D, false, false>::kStages;
   static constexpr int q_full = 0;               // + t
   static constexpr int k_full = 2;               // + stage
   static constexpr int k_empty = k_full + kS;
@@ -95,7 +106,9 @@ struct FwdBars {
   static constexpr int o_free = q_empty + 2;     // + t: the epilogue has read O_t, the next item may overwrite it
   static constexpr int work_full = o_free + 2;   // + slot: the producer has fetched a work item
   static constexpr int work_empty = work_full + 2;  // + slot: every consumer has read it
-  static constexpr int count = work_empty + 2;
+  static constexpr int stage_full = work_empty + 2;   // + t: every row of a staging block is written (128 arrivals)
+  static constexpr int stage_free = stage_full + 2;   // + t: the tile store has read the block
+  static constexpr int count = stage_free + 2;
 };
 
 // Build-time diagnostic (-DLIMN_TRACE): one CTA records clock64() at each step of its pipeline into a
@@ -130,8 +143,8 @@ struct FwdParams {
 template <int D, bool kCausal, bool kFp16, bool kMask>
 __global__ void __launch_bounds__(kThreads, 1)
 sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                const __grid_constant__ CUtensorMap map_v, const FwdParams prm) {
-  using L = FwdLayout<D>;
+                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o, const FwdParams prm) {
+  using L = FwdLayout<D, kCausal, kMask>;
   using B = FwdBars<D>;
   extern __shared__ unsigned char smem_unaligned[];
   __shared__ uint32_t tmem_slot;
@@ -176,7 +189,8 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (threadIdx.x == 0) {
     for (int i = 0; i < B::count; ++i) {
       unsigned arrivals = 1u;
-      if ((i >= B::p_full && i < B::p_full + 2) || (i >= B::p_half && i < B::p_half + 2) || (i >= B::o_free && i < B::o_free + 2))
+      if ((i >= B::p_full && i < B::p_full + 2) || (i >= B::p_half && i < B::p_half + 2) || (i >= B::o_free && i < B::o_free + 2) ||
+          (i >= B::stage_full && i < B::stage_full + 2))
         arrivals = 128u;                                           // every thread of a softmax group
       if (i >= B::work_empty && i < B::work_empty + 2) arrivals = 9u;  // the MMA warp and the eight softmax warps
       mbar_init(bar(i), arrivals);
@@ -387,6 +401,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const uint64_t sl2_2 = f2_pack(sl2, sl2);
     unsigned tiles = 0;   // key tiles this group has been through, over all items
     unsigned o_uses = 0;  // items this group has finished
+    unsigned stores = 0;  // staging blocks this group has handed to TMA
     // Key mask: a hidden key is a score of -inf for every row. Each warp keeps its own copy of the tile's 128
     // flags in shared memory as an additive 0 / -inf, each lane fetching four of them one tile ahead of use.
     float* bias = reinterpret_cast<float*>(smem_unaligned + (base - raw) + L::kBiasOff) + warp * 256;
@@ -535,6 +550,56 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tc_fence_after_sync();
       const float inv = 1.f / l;
       const long long out_row = static_cast<long long>(problem) * prm.t_q + row;  // in L, which is always dense
+      if constexpr (L::kTileStore) {
+        // O goes out as tile stores: every thread leaves its row, rounded, in the group's staging block (in the
+        // swizzled layout, so the 32 rows of a warp fall on distinct banks), and one thread hands the block to TMA,
+        // which writes whole 128-byte rows and leaves out the rows and columns the tensor does not have. (A thread
+        // storing its own row in 16-byte pieces costs the load/store unit 32 transactions per instruction.)
+        const uint32_t stage = base + L::kStageOff + t * L::kAtomBytes;
+        const bool leader = (warp & 3) == 0 && lane == 0;
+#pragma unroll
+        for (int blk = 0; blk < D / 64 && ok; ++blk, ++stores) {
+          // the store before this one has read the block: the thread that issued it says so (waits are bounded,
+          // like every wait here: a group whose warps disagree about going on must not hang on one another)
+          if (leader) {
+            tma_store_wait_read();
+            mbar_arrive(bar(B::stage_free + t));
+          }
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(B::stage_free + t), stores & 1u, prm.status, 0x0320u | t));
+          if (!ok) break;
+#pragma unroll
+          for (int cc = 0; cc < 2; ++cc) {
+            uint32_t o[32];
+            tmem_ld32(t_o + 64 * blk + 32 * cc, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int v4 = 0; v4 < 4; ++v4) {
+              uint32_t w[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float a = __uint_as_float(o[v4 * 8 + 2 * i]) * inv;
+                const float b = __uint_as_float(o[v4 * 8 + 2 * i + 1]) * inv;
+                w[i] = kFp16 ? pack_f16(a, b) : pack_bf16(a, b);
+              }
+              st_shared_v4(swizzled_piece(stage, row_in_tile, cc * 4 + v4), w[0], w[1], w[2], w[3]);
+            }
+          }
+          if (blk == D / 64 - 1) {
+            // O_t is in registers or staged: the next item's first product may overwrite it
+            tc_fence_before_sync();
+            mbar_arrive(bar(B::o_free + t));
+          }
+          fence_async_shared();
+          mbar_arrive(bar(B::stage_full + t));
+          if (leader) {
+            if (mbar_wait(bar(B::stage_full + t), stores & 1u, prm.status, 0x0330u | t)) {
+              tma_store_4d(&map_o, stage, 64 * blk, item.q0[t], item.head, item.batch);
+              tma_store_commit();
+            }
+          }
+        }
+        if (row < prm.t_q) prm.lse[out_row] = m * prm.scale + logf(l);
+      } else {
       const long long out_at = item.batch * prm.out_strides.batch + item.head * prm.out_strides.head + row * prm.out_strides.row;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
@@ -560,9 +625,12 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // O_t is in registers or stored: the next item's first product may overwrite it
       tc_fence_before_sync();
       mbar_arrive(bar(B::o_free + t));
+      }
       ++o_uses;
     }
     }  // items
+    // the last tile store must have read its staging block before the CTA gives its shared memory back
+    if (L::kTileStore && (warp & 3) == 0 && lane == 0) tma_store_wait_read();
   }
 
   // ---- teardown ----
@@ -587,12 +655,13 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
 template <int D, bool kCausal, bool kFp16, bool kMask>
 int launch_fwd(const Problem& p) {
-  using L = FwdLayout<D>;
-  CUtensorMap map_q, map_k, map_v;
+  using L = FwdLayout<D, kCausal, kMask>;
+  CUtensorMap map_q, map_k, map_v, map_o;
   const int heads = p.heads > 0 ? p.heads : static_cast<int>(p.bh), batch = static_cast<int>(p.bh / heads);
   if (int rc = make_tile_map(&map_q, p.q, kFp16, batch, heads, p.t_q, p.hd, kTileRows, operand_strides(p, kOpQ, heads, p.t_q, p.hd))) return rc;
   if (int rc = make_tile_map(&map_k, p.k, kFp16, batch, heads, p.t_k, p.hd, kTileRows, operand_strides(p, kOpK, heads, p.t_k, p.hd))) return rc;
   if (int rc = make_tile_map(&map_v, p.v, kFp16, batch, heads, p.t_k, p.hd_v, kTileRows, operand_strides(p, kOpV, heads, p.t_k, p.hd_v))) return rc;
+  if (int rc = make_tile_map(&map_o, p.out, kFp16, batch, heads, p.t_q, p.hd_v, kTileRows, operand_strides(p, kOpOut, heads, p.t_q, p.hd_v))) return rc;
   FwdParams prm;
   prm.out = p.out;
   prm.heads = heads;
@@ -634,7 +703,7 @@ int launch_fwd(const Problem& p) {
               "sizing shared memory for the sdpa kernel");
     sized[device] = true;
   }
-  LIMN_CUDA(launch_overlapped(kernel, dim3(static_cast<unsigned>(ctas)), dim3(kThreads), L::kBytes, p.stream, map_q, map_k, map_v, prm),
+  LIMN_CUDA(launch_overlapped(kernel, dim3(static_cast<unsigned>(ctas)), dim3(kThreads), L::kBytes, p.stream, map_q, map_k, map_v, map_o, prm),
             "launching the sdpa kernel");
   note_launches(1);
   return LIMN_B200_OK;

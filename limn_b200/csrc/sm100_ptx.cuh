@@ -129,6 +129,26 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
 // ---- tensor memory ----
 // Allocate `cols` columns (power of two, 32..512); the base address lands in *slot (shared).
 // Executed by one whole warp; the same warp frees it.
+// A tile store from shared memory (in the tensor map's box layout) to global memory, asynchronous: rows and columns
+// of the box that lie outside the tensor are not written. Stores issued by a thread form groups (tma_store_commit);
+// tma_store_wait_read returns once all of that thread's groups have finished reading shared memory.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Where the 16-byte piece `piece` (0..7) of row `row` lies in a 128-byte-swizzled tile of 128-byte rows at `tile`
+// (1024-byte aligned): the layout TMA reads and writes with CU_TENSOR_MAP_SWIZZLE_128B.
+__device__ __forceinline__ uint32_t swizzled_piece(uint32_t tile, int row, int piece) {
+  return tile + static_cast<uint32_t>(row) * 128u + (static_cast<uint32_t>(piece ^ (row & 7)) << 4);
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
 __device__ __forceinline__ void tmem_alloc(uint32_t slot, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(cols) : "memory");
 }
