@@ -70,9 +70,16 @@ struct BwdLayout {
   static constexpr int kHeldOff = 0;                               // two resident tiles
   static constexpr int kStreamAOff = 2 * kTileBytes;               // ring of the first streamed tile (K, or Q)
   static constexpr int kStreamBOff = kStreamAOff + kStagesA * kTileBytes;  // ring of the second (V, or dO)
-  static constexpr int kStatOff = kStreamBOff + kStagesB * kTileBytes;
+  // The dK/dV pass at head dim 64 (where shared memory has the room): the epilogue leaves dV and dK here as blocks of
+  // 128 rows x 128 B in the swizzled layout and TMA stores them, instead of every thread storing its own row in
+  // 16-byte pieces (32 transactions per instruction for the load/store unit: 2 000 clocks per work item). Measured:
+  // 13 % off the pass at S = 256, 2 % at S = 2048. In the dQ pass, where a thread stores half a row, the hand-overs
+  // cost as much as they save (+2 % at S = 2048), so it keeps storing from registers.
+  static constexpr bool kTileStore = D == 64 && kKV;
+  static constexpr int kStoreOff = kStreamBOff + kStagesB * kTileBytes;
+  static constexpr int kStatOff = kStoreOff + (kTileStore ? (kKV ? 2 : 1) * kAtomBytes : 0);
   static constexpr int kBarOff = kStatOff + ((kKV || kMask) ? 8 * 2 * 2 * 64 * 4 : 0);  // per warp [2 buffers][128 floats]: statistics (dK/dV pass) or key-mask bias (dQ pass)
-  static constexpr int kBytes = kBarOff + 256 + 1024;
+  static constexpr int kBytes = kBarOff + 512 + 1024;
   static_assert(kBytes <= 227 * 1024, "shared memory per CTA");
   // tensor-memory columns
   static constexpr int kSCol = 0;      // S (or S^T); P^T overlays it as 16-bit
@@ -103,7 +110,9 @@ struct BwdBars {
   static constexpr int work_empty = work_full + 2;  // + slot: every consumer has read it
   static constexpr int delta_full = work_empty + 2;   // + slot, fused dQ pass: the item's row statistics are in shared memory (64 arrivals)
   static constexpr int delta_empty = delta_full + 2;  // + slot: the elementwise threads have taken them (256 arrivals)
-  static constexpr int count = delta_empty + 2;
+  static constexpr int store_full = delta_empty + 2;  // tile-store epilogue: every row of the staging blocks is written (256 arrivals)
+  static constexpr int store_free = store_full + 1;   // the tile stores before have read the blocks
+  static constexpr int count = store_free + 1;
 };
 
 // Build-time diagnostic (-DLIMN_TRACE): one CTA records clock64() at each step of its pipeline into a
@@ -205,7 +214,7 @@ template <int D, bool kCausal, bool kFp16, bool kKV, bool kEarly, bool kSeq, boo
 __global__ void __launch_bounds__(kThreads, 1)
 sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-                const BwdParams prm) {
+                const __grid_constant__ CUtensorMap map_out0, const __grid_constant__ CUtensorMap map_out1, const BwdParams prm) {
   using L = BwdLayout<D, kKV, kMask>;
   using B = BwdBars<D, kKV, kMask>;
   extern __shared__ unsigned char smem_unaligned[];
@@ -262,7 +271,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         // s_full + 1 doubles as "scores read into registers", ds_full + 1 as "products done" (one commit)
         if (i == B::s_full + 1 || i == B::ds_full) arrivals = 256u;
       }
-      if (i == B::acc_free) arrivals = 256u;
+      if (i == B::acc_free || i == B::store_full) arrivals = 256u;
       // the MMA warp and the eight elementwise warps, and in the fused dQ pass the two warps that compute delta
       if (i == B::work_empty || i == B::work_empty + 1) arrivals = (!kKV && prm.o_rows != nullptr) ? 11u : 9u;
       if (i == B::delta_full || i == B::delta_full + 1) arrivals = 64u;    // every thread of the two warps that wrote them
@@ -795,7 +804,50 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     Fetched upcoming_head = head;
     if (ok) ok = take_item(n_item + 1, upcoming, upcoming_item, upcoming_head);
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(B::acc_full), n_item & 1u, prm.status, 0x1310u));
-    if (ok) {
+    if (ok && L::kTileStore) {
+      tc_fence_after_sync();
+      // the stores of the item before have read the staging blocks: the thread that issued them says so
+      const bool leader = threadIdx.x == 0;
+      if (leader) {
+        tma_store_wait_read();
+        mbar_arrive(bar(B::store_free));
+      }
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(B::store_free), n_item & 1u, prm.status, 0x1350u));
+      if (ok) {
+        // dK/dV pass: group 0 stages this key's dV row, group 1 its dK row, a block each; dQ pass: each group half
+        // of this query's dQ row, in the one block
+        const uint32_t block = base + L::kStoreOff + (kKV ? group * L::kAtomBytes : 0);
+        const float mul = (kKV && group == 0) ? 1.f : prm.scale;
+#pragma unroll
+        for (int c = 0; c < (kKV ? 2 : 1); ++c) {
+          const int col = kKV ? 32 * c : group * 32;
+          uint32_t acc[32];
+          tmem_ld32(tmem + lane_base + ((kKV && group == 1) ? L::kAcc1 : L::kAcc0) + col, acc);
+          tmem_ld_wait();
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float a = __uint_as_float(acc[v4 * 8 + 2 * i]) * mul;
+              const float b = __uint_as_float(acc[v4 * 8 + 2 * i + 1]) * mul;
+              w[i] = kFp16 ? pack_f16(a, b) : pack_bf16(a, b);
+            }
+            st_shared_v4(swizzled_piece(block, r, (col >> 3) + v4), w[0], w[1], w[2], w[3]);
+          }
+        }
+        // the accumulators are in registers or staged: the next item's first products may overwrite them
+        tc_fence_before_sync();
+        mbar_arrive(bar(B::acc_free));
+        fence_async_shared();
+        mbar_arrive(bar(B::store_full));
+        if (leader && mbar_wait(bar(B::store_full), n_item & 1u, prm.status, 0x1360u)) {
+          tma_store_4d(&map_out0, base + L::kStoreOff + (kKV ? L::kAtomBytes : 0), 0, own0, item.head, item.batch);  // dQ, or dK
+          if (kKV) tma_store_4d(&map_out1, base + L::kStoreOff, 0, own0, item.head, item.batch);                      // dV
+          tma_store_commit();
+        }
+      }
+    } else if (ok) {
       tc_fence_after_sync();
       const int row = own0 + r;
       if (kKV) {
@@ -833,6 +885,8 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     done += count;
     index = upcoming, item = upcoming_item, head = upcoming_head;
     }  // items
+    // the last tile stores must have read their staging blocks before the CTA gives its shared memory back
+    if (L::kTileStore && threadIdx.x == 0) tma_store_wait_read();
   }
 
   else if (!kKV && prm.o_rows != nullptr) {
@@ -895,6 +949,15 @@ int launch_bwd(const Problem& p) {
   if (int rc = make_tile_map(&map_k, p.k, kFp16, batch, heads, p.t_k, p.hd, kTile, operand_strides(p, kOpK, heads, p.t_k, p.hd))) return rc;
   if (int rc = make_tile_map(&map_v, p.v, kFp16, batch, heads, p.t_k, p.hd_v, kTile, operand_strides(p, kOpV, heads, p.t_k, p.hd_v))) return rc;
   if (int rc = make_tile_map(&map_do, p.dout, kFp16, batch, heads, p.t_q, p.hd_v, kTile, operand_strides(p, kOpDout, heads, p.t_q, p.hd_v))) return rc;
+  CUtensorMap map_out0 = map_q, map_out1 = map_q;  // only read by the kernels that store tiles
+  if (L::kTileStore) {
+    if (kKV) {
+      if (int rc = make_tile_map(&map_out0, p.dk, kFp16, batch, heads, p.t_k, p.hd, kTile, operand_strides(p, kOpDk, heads, p.t_k, p.hd))) return rc;
+      if (int rc = make_tile_map(&map_out1, p.dv, kFp16, batch, heads, p.t_k, p.hd_v, kTile, operand_strides(p, kOpDv, heads, p.t_k, p.hd_v))) return rc;
+    } else {
+      if (int rc = make_tile_map(&map_out0, p.dq, kFp16, batch, heads, p.t_q, p.hd, kTile, operand_strides(p, kOpDq, heads, p.t_q, p.hd))) return rc;
+    }
+  }
   BwdParams prm;
   prm.mask = static_cast<const unsigned short*>(p.mask);
   prm.lse = static_cast<const float*>(p.lse_in);
@@ -951,7 +1014,7 @@ int launch_bwd(const Problem& p) {
               "sizing shared memory for an sdpa backward kernel");
     sized[device] = true;
   }
-  LIMN_CUDA(launch_overlapped(kernel, dim3(static_cast<unsigned>(ctas)), dim3(kThreads), L::kBytes, p.stream, map_q, map_k, map_v, map_do, prm),
+  LIMN_CUDA(launch_overlapped(kernel, dim3(static_cast<unsigned>(ctas)), dim3(kThreads), L::kBytes, p.stream, map_q, map_k, map_v, map_do, map_out0, map_out1, prm),
             "launching an sdpa backward kernel");
   note_launches(1);
   return LIMN_B200_OK;
