@@ -47,6 +47,16 @@ constexpr int kTile = 128;
 // Ten warps work; the CTA is launched with twelve because the compiler spills less in the elementwise loop at
 // this block size (measured: 1 to 2 % faster). Warps 10 and 11 go straight to the final barrier.
 constexpr int kThreads = 384;
+#ifndef LIMN_BWD_KV_THREADS
+#define LIMN_BWD_KV_THREADS 352
+#endif
+// The dK/dV pass never uses warps 10 and 11 (the dQ pass does, when it computes the row statistics itself), and
+// its elementwise loop comes out of the compiler a little better with one spare warp than with two (1 % at head dim
+// 64, nothing at 128; the dQ pass is 2 to 4 % slower that way and keeps its twelve).
+template <bool kKV>
+constexpr int bwd_threads() {
+  return kKV ? LIMN_BWD_KV_THREADS : kThreads;
+}
 constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;
 constexpr uint32_t kTmemCols = 512;
@@ -211,7 +221,7 @@ __device__ __forceinline__ float row_dot(const void* a_row, const void* b_row, i
 // S^T and dP^T take turns in one 128-column region, S^T first, dP^T as soon as S^T is in registers, so that
 // 128 columns are left for the operands and every MMA is full width.
 template <int D, bool kCausal, bool kFp16, bool kKV, bool kEarly, bool kSeq, bool kMask>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__((bwd_threads<kKV>()), 1)
 sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                 const __grid_constant__ CUtensorMap map_out0, const __grid_constant__ CUtensorMap map_out1, const BwdParams prm) {
@@ -1052,7 +1062,7 @@ int launch_bwd(const Problem& p) {
               "sizing shared memory for an sdpa backward kernel");
     sized[device] = true;
   }
-  LIMN_CUDA(launch_overlapped(kernel, dim3(static_cast<unsigned>(ctas)), dim3(kThreads), L::kBytes, p.stream, map_q, map_k, map_v, map_do, map_out0, map_out1, prm),
+  LIMN_CUDA(launch_overlapped(kernel, dim3(static_cast<unsigned>(ctas)), dim3(bwd_threads<kKV>()), L::kBytes, p.stream, map_q, map_k, map_v, map_do, map_out0, map_out1, prm),
             "launching an sdpa backward kernel");
   note_launches(1);
   return LIMN_B200_OK;

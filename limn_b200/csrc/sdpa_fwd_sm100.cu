@@ -38,10 +38,15 @@ using namespace ptx;
 
 constexpr int kTileRows = 128;   // query rows per Q tile, keys per K/V tile
 constexpr int kQTiles = 2;       // Q tiles per CTA
-// Ten warps work; the CTA is launched with twelve because the compiler's register allocation for the softmax
-// loop comes out with far fewer spills at this block size (measured: 3 to 10 % faster). Warps 10 and 11 go
-// straight to the final barrier.
-constexpr int kThreads = 384;
+// Ten warps work, but the block size decides how the compiler allocates registers in the softmax loop (all sizes
+// end at 168 registers; what differs is what is spilled where), and the best size differs by instantiation.
+// Measured on B200: head dim 128 under a causal mask, 11 warps (0.7 % over 12, 8 % over 10); without a key mask
+// otherwise, 10 warps (head dim 64: 1 to 5 % over 12; head dim 128 without a causal mask: 1 %); the key-mask kernels
+// stay at the 12 they were tuned with. The spare warps go straight to the final barrier.
+template <int D, bool kCausal, bool kMask>
+constexpr int fwd_threads() {
+  return kMask ? 384 : (D == 128 && kCausal) ? 352 : 320;
+}
 constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;
 constexpr uint32_t kTmemCols = 512;
@@ -141,7 +146,7 @@ struct FwdParams {
 };
 
 template <int D, bool kCausal, bool kFp16, bool kMask>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__((fwd_threads<D, kCausal, kMask>()), 1)
 sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o, const FwdParams prm) {
   using L = FwdLayout<D, kCausal, kMask>;
@@ -703,7 +708,7 @@ int launch_fwd(const Problem& p) {
               "sizing shared memory for the sdpa kernel");
     sized[device] = true;
   }
-  LIMN_CUDA(launch_overlapped(kernel, dim3(static_cast<unsigned>(ctas)), dim3(kThreads), L::kBytes, p.stream, map_q, map_k, map_v, map_o, prm),
+  LIMN_CUDA(launch_overlapped(kernel, dim3(static_cast<unsigned>(ctas)), dim3(fwd_threads<D, kCausal, kMask>()), L::kBytes, p.stream, map_q, map_k, map_v, map_o, prm),
             "launching the sdpa kernel");
   note_launches(1);
   return LIMN_B200_OK;
