@@ -63,7 +63,9 @@ int limn_b200_sdpa_bwd_q(const void* q, const void* k, const void* v, const void
                          int causal, double scale, void* stream);
 
 /* "sdpa_bwd_q" with the row dot folded in: the same dQ as limn_b200_sdpa_delta followed by limn_b200_sdpa_bwd_q,
- * one launch and one pass over O and dO fewer. Replaces the pair limn's frontend schedules between the forward and
+ * one launch and one pass over O and dO fewer where that is the faster way (short sequences); for dense operands
+ * with more than 512 keys the call runs the row-dot kernel and the dQ kernel itself, which is faster there. Either
+ * way one call. Replaces the pair limn's frontend schedules between the forward and
  * the backward ops (the reduce of limn/tensor.py:705-706 and emit_sdpa_bwd_q, limn/cuda_emit.py:968-1005).
  *   out is the forward's O (bh, t_q, hd_v), an input here; delta (bh, t_q) in the statistics dtype is an OUTPUT:
  *   every CTA computes the statistic of the query rows it owns from their rows of O and dO and leaves it there for

@@ -216,7 +216,18 @@ int dispatch_op(Op op, const char* name, const Problem& p) {
   if (int rc = validate_op(op, name, p)) return rc;
   if (p.bh == 0) return LIMN_B200_OK;
   if (decode_serves(op, p)) return decode_launch(p);
-  if (tcgen05_serves(op, p)) return tcgen05_launch(op, p);
+  if (tcgen05_serves(op, p)) {
+    // The dQ kernel can compute the row statistic on its spare warps, which saves a launch and a pass over O and dO:
+    // 7 % at S = 256. From a few key tiles per work item on, the separate row-dot kernel in front of it is the faster
+    // way to the same delta and dQ (2.5 to 3 % at S = 2048 and 3000), so dense operands of that size take it.
+    if (op == Op::BwdQ && p.fuse_delta && !p.strided && p.layout == LIMN_B200_BHTD && p.t_k > 512) {
+      if (int rc = general_delta(p.out, p.dout, const_cast<void*>(p.delta), p.dtype, p.bh * p.t_q, p.hd_v, p.stream)) return rc;
+      Problem unfused = p;
+      unfused.fuse_delta = false;
+      return tcgen05_launch(op, unfused);
+    }
+    return tcgen05_launch(op, p);
+  }
   if (op == Op::BwdQ && p.fuse_delta) {
     // the general kernels read delta: fill it first, as the unfused sequence would
     if (int rc = general_delta(p.out, p.dout, const_cast<void*>(p.delta), p.dtype, p.bh * p.t_q, p.hd_v, p.stream)) return rc;
