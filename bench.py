@@ -106,9 +106,9 @@ def forward_traffic(workload: str, problems: int) -> tuple[float | None, str]:
     proportional (every problem's tensors cross HBM once). (None, why) where no capture exists."""
     captured = {
         # workload: (problems in the capture, dram bytes read, dram bytes written, what the capture was)
-        "prefill_4k": (128, 406.515968e6, 119.008256e6,
+        "prefill_4k": (128, 406.098944e6, 121.099264e6,
                        "128-problem capture (402.7 MB of Q, K, V; 136.3 MB of O and L, more than L2 holds): reads are the inputs "
-                       "once; 17 MB of the output had not left L2 when the counters stopped, so the write side is a lower bound"),
+                       "once; 15 MB of the output had not left L2 when the counters stopped, so the write side is a lower bound"),
         "encoder_2k": (128, 102.376448e6, 18.868224e6, "128-problem capture; its 34 MB of output fit in L2, so the write side is a lower bound"),
     }
     if workload not in captured:

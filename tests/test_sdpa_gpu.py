@@ -211,6 +211,32 @@ def test_masked_row_without_a_visible_key_on_the_tensor_core_path(dev):
     assert float(np.abs(lse[:, 5:] - want_lse[:, 5:]).max()) <= 1e-3
 
 
+def test_the_fused_dq_entry_picks_its_way_by_size():
+    """limn_b200_sdpa_bwd_q_fused computes the row statistic inside the dQ kernel up to 512 keys (one launch) and runs
+    the row-dot kernel in front of the plain dQ kernel beyond (two launches); delta and dQ are the same either way."""
+    from limn_b200 import runtime
+    from limn_b200._lib import check, lib
+
+    L = lib()
+    rng = np.random.default_rng(9)
+    for t, launches in ((512, 1), (640, 2)):
+        q, k, v, do = (runtime.upload(rng.standard_normal((2, t, 64)).astype(np.float32).astype(BF16)) for _ in range(4))
+        out, dq_a, dq_b = (runtime.empty(2 * t * 64 * 2) for _ in range(3))
+        lse, delta_a, delta_b = (runtime.empty(2 * t * 4) for _ in range(3))
+        tail = (2, 2, t, t, 64, 64, 1, 0.125, None)
+        check(L.limn_b200_sdpa_fwd(q.ptr, k.ptr, v.ptr, None, out.ptr, lse.ptr, *tail), "sdpa")
+        check(L.limn_b200_sdpa_bwd_q_fused(q.ptr, k.ptr, v.ptr, out.ptr, do.ptr, lse.ptr, None, dq_a.ptr, delta_a.ptr, *tail), "fused dq")
+        assert L.limn_b200_last_launch_count() == launches, t
+        check(L.limn_b200_sdpa_delta(out.ptr, do.ptr, delta_b.ptr, 2, 2 * t, 64, None), "row dot")
+        check(L.limn_b200_sdpa_bwd_q(q.ptr, k.ptr, v.ptr, do.ptr, lse.ptr, delta_b.ptr, None, dq_b.ptr, *tail), "dq")
+        runtime.synchronize()
+        assert runtime.device_status() == 0
+        got = runtime.download(dq_a, BF16, (2, t, 64)).astype(np.float32)
+        want = runtime.download(dq_b, BF16, (2, t, 64)).astype(np.float32)
+        np.testing.assert_allclose(got, want, rtol=2**-7, atol=2e-3)
+        np.testing.assert_allclose(runtime.download(delta_a, np.float32, (2, t)), runtime.download(delta_b, np.float32, (2, t)), rtol=1e-5, atol=1e-5)
+
+
 TILED_CASES = [
     # id, dtype, q, k, v shapes, causal, mask kind
     ("f32 d64 causal 256 batch (a GPT layer in float32)", np.float32, (4, 8, 256, 64), (4, 8, 256, 64), (4, 8, 256, 64), True, None),
