@@ -434,11 +434,16 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     float flags[4] = {0.f, 0.f, 0.f, 0.f};
     if (kMask) fetch_flags(problem, 0, flags);
     for (int j = 0; j < n; ++j, ++tiles) {
+      // a tile none of whose keys is hidden (every tile but the last few of a padded batch) takes no bias at all
+      bool any_hidden = false;
       if (kMask) {
-        float* mine = bias + (j & 1) * 128;
+        any_hidden = __any_sync(0xffffffffu, (flags[0] + flags[1]) + (flags[2] + flags[3]) != 0.f);
+        if (any_hidden) {
+          float* mine = bias + (j & 1) * 128;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) mine[32 * c + lane] = flags[c];
-        __syncwarp();
+          for (int c = 0; c < 4; ++c) mine[32 * c + lane] = flags[c];
+          __syncwarp();
+        }
         if (j + 1 < n) fetch_flags(problem, (j + 1) * kTileRows, flags);
       }
       ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full + t), tiles & 1u, prm.status, 0x0300u | t));  // warp-uniform: the tensor-memory ops below are warp-wide
@@ -462,7 +467,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           for (int i = 0; i < 32; ++i)
             if (c * 32 + i >= limit) s[c][i] = 0xff800000u;  // -inf
       }
-      if (kMask) {
+      if (kMask && any_hidden) {
         const float2* mine = reinterpret_cast<const float2*>(bias + (j & 1) * 128);
 #pragma unroll
         for (int c = 0; c < 4; ++c)
