@@ -75,7 +75,7 @@ struct BwdLayout {
   static constexpr int kAtomBytes = kTile * 128;
   // ring depths of the two streamed tiles. In the dQ pass at head dim 128 the V tile is only read by the
   // scores and leaves early, so two slots do for it and K gets the third that shared memory has room for.
-  static constexpr int kStagesA = D == 128 ? ((kKV || kMask) ? 2 : 3) : 3;  // a key mask's staging takes the room of the third slot
+  static constexpr int kStagesA = D == 128 ? (kKV ? 2 : 3) : 3;
   static constexpr int kStagesB = D == 128 ? 2 : 3;
   static constexpr int kHeldOff = 0;                               // two resident tiles
   static constexpr int kStreamAOff = 2 * kTileBytes;               // ring of the first streamed tile (K, or Q)
@@ -88,7 +88,7 @@ struct BwdLayout {
   static constexpr bool kTileStore = D == 64 && kKV;
   static constexpr int kStoreOff = kStreamBOff + kStagesB * kTileBytes;
   static constexpr int kStatOff = kStoreOff + (kTileStore ? (kKV ? 2 : 1) * kAtomBytes : 0);
-  static constexpr int kBarOff = kStatOff + ((kKV || kMask) ? 8 * 2 * 2 * 64 * 4 : 0);  // per warp [2 buffers][128 floats]: statistics (dK/dV pass) or key-mask bias (dQ pass)
+  static constexpr int kBarOff = kStatOff + (kKV ? 8 * 2 * 2 * 64 * 4 : 0);  // dK/dV pass, per warp [2 buffers][128 floats]: statistics of the streamed queries
   static constexpr int kBytes = kBarOff + 512 + 1024;
   static_assert(kBytes <= 227 * 1024, "shared memory per CTA");
   // tensor-memory columns
@@ -688,9 +688,12 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const int other0 = (first + it) * kTile;  // first key (dQ pass) or first query (dK/dV pass) of the streamed tile
       // per warp: [2 buffers][-L log2e, -delta][64 columns]
       float* st = stat + (warp * 2 + (g & 1)) * (2 * 64);
+      // dQ pass under a key mask: which of the group's 64 keys of this tile are hidden, as two words in registers
+      // (a ballot over the flags each lane fetched a tile ahead); most tiles of a padded batch have none
+      unsigned hidden_lo = 0u, hidden_hi = 0u;
       if (kMask && !kKV) {
-        st[lane] = col_bias0, st[lane + 32] = col_bias1;
-        __syncwarp();
+        hidden_lo = __ballot_sync(0xffffffffu, col_bias0 != 0.f);
+        hidden_hi = __ballot_sync(0xffffffffu, col_bias1 != 0.f);
         if (it + 1 < count) {
           col_bias0 = key_bias(other0 + kTile + group * 64 + lane);
           col_bias1 = key_bias(other0 + kTile + group * 64 + lane + 32);
@@ -791,7 +794,8 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         TRACE_EVENT(3);
         const bool diagonal = kCausal && other0 == own0;
         const bool ragged = !kKV && other0 + kTile > prm.t_k;
-        if (diagonal || ragged) {
+        const bool masked = kMask && !kKV && (hidden_lo | hidden_hi) != 0u;
+        if (diagonal || ragged || masked) {
 #pragma unroll
           for (int c = 0; c < 2; ++c)
 #pragma unroll
@@ -800,6 +804,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
               bool hidden = false;
               if (diagonal) hidden = kKV ? (col < r) : (col > r);   // a key index must not exceed the query index
               if (ragged) hidden = hidden || (other0 + col >= prm.t_k);
+              if (kMask && !kKV) hidden = hidden || (((c == 0 ? hidden_lo : hidden_hi) >> e) & 1u) != 0u;
               if (hidden) s[c][e] = 0xff800000u;  // -inf: the probability becomes exactly 0
             }
         }
@@ -819,12 +824,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
               neg_delta = row_neg_delta;
             }
             if (kMask) {
-              if (kKV) {
-                neg_l2 = f2_add(neg_l2, row_bias2);
-              } else {
-                const float2 b = *reinterpret_cast<const float2*>(st + c * 32 + e);
-                neg_l2 = f2_add(neg_l2, f2_pack(b.x, b.y));
-              }
+              if (kKV) neg_l2 = f2_add(neg_l2, row_bias2);  // (the dQ pass has rewritten its hidden keys' scores above)
             }
             const uint64_t x2 = f2_fma(f2_pack_bits(s[c][e], s[c][e + 1]), sl2_2, neg_l2);
             float p0, p1;
