@@ -672,15 +672,20 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const bool live = key < prm.t_k && (prm.mask[static_cast<long long>(problem) * prm.t_k + key] & 0x7fffu) != 0;
       return live ? 0.f : -INFINITY;
     };
+    // (dQ pass: the flags stay as loaded until the next tile needs them. A warp issues in order, so turning them
+    // into anything right after the load would stall it for the load's latency, every tile.)
+    auto key_flag = [&](int key) -> unsigned {
+      return key < prm.t_k ? prm.mask[static_cast<long long>(problem) * prm.t_k + key] : 0u;  // past the end: hidden
+    };
     uint64_t row_bias2 = 0;
-    float col_bias0 = 0.f, col_bias1 = 0.f;
+    unsigned col_flag0 = 1u, col_flag1 = 1u;
     if (kMask) {
       if (kKV) {
         const float b = key_bias(own0 + r);
         row_bias2 = f2_pack(b, b);
       } else {
-        col_bias0 = key_bias(first * kTile + group * 64 + lane);
-        col_bias1 = key_bias(first * kTile + group * 64 + lane + 32);
+        col_flag0 = key_flag(first * kTile + group * 64 + lane);
+        col_flag1 = key_flag(first * kTile + group * 64 + lane + 32);
       }
     }
     for (int it = 0; it < count; ++it) {
@@ -692,11 +697,11 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // (a ballot over the flags each lane fetched a tile ahead); most tiles of a padded batch have none
       unsigned hidden_lo = 0u, hidden_hi = 0u;
       if (kMask && !kKV) {
-        hidden_lo = __ballot_sync(0xffffffffu, col_bias0 != 0.f);
-        hidden_hi = __ballot_sync(0xffffffffu, col_bias1 != 0.f);
+        hidden_lo = __ballot_sync(0xffffffffu, (col_flag0 & 0x7fffu) == 0u);
+        hidden_hi = __ballot_sync(0xffffffffu, (col_flag1 & 0x7fffu) == 0u);
         if (it + 1 < count) {
-          col_bias0 = key_bias(other0 + kTile + group * 64 + lane);
-          col_bias1 = key_bias(other0 + kTile + group * 64 + lane + 32);
+          col_flag0 = key_flag(other0 + kTile + group * 64 + lane);
+          col_flag1 = key_flag(other0 + kTile + group * 64 + lane + 32);
         }
       }
       if (kKV) {

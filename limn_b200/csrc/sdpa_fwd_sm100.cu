@@ -410,12 +410,13 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     // Key mask: a hidden key is a score of -inf for every row. Each warp keeps its own copy of the tile's 128
     // flags in shared memory as an additive 0 / -inf, each lane fetching four of them one tile ahead of use.
     float* bias = reinterpret_cast<float*>(smem_unaligned + (base - raw) + L::kBiasOff) + warp * 256;
-    auto fetch_flags = [&](int problem, int kv0, float (&out4)[4]) {
+    // (the flags stay as loaded until the next tile needs them: a warp issues in order, so turning them into anything
+    // right after the load would stall it for the load's latency, every tile)
+    auto fetch_flags = [&](int problem, int kv0, unsigned (&out4)[4]) {
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int key = kv0 + 32 * c + lane;
-        const bool live = key < prm.t_k && (prm.mask[static_cast<long long>(problem) * prm.t_k + key] & 0x7fffu) != 0;
-        out4[c] = live ? 0.f : -INFINITY;
+        out4[c] = key < prm.t_k ? prm.mask[static_cast<long long>(problem) * prm.t_k + key] : 0u;  // past the end: hidden
       }
     };
     for (unsigned n_item = 0; ok; ++n_item) {
@@ -431,17 +432,20 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     if (n == 0) continue;
     const int row = item.q0[t] + row_in_tile;
     float m = -INFINITY, l = 0.f;
-    float flags[4] = {0.f, 0.f, 0.f, 0.f};
+    unsigned flags[4] = {1u, 1u, 1u, 1u};
     if (kMask) fetch_flags(problem, 0, flags);
     for (int j = 0; j < n; ++j, ++tiles) {
       // a tile none of whose keys is hidden (every tile but the last few of a padded batch) takes no bias at all
       bool any_hidden = false;
       if (kMask) {
-        any_hidden = __any_sync(0xffffffffu, (flags[0] + flags[1]) + (flags[2] + flags[3]) != 0.f);
+        bool hidden[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) hidden[c] = (flags[c] & 0x7fffu) == 0u;
+        any_hidden = __any_sync(0xffffffffu, hidden[0] || hidden[1] || hidden[2] || hidden[3]);
         if (any_hidden) {
           float* mine = bias + (j & 1) * 128;
 #pragma unroll
-          for (int c = 0; c < 4; ++c) mine[32 * c + lane] = flags[c];
+          for (int c = 0; c < 4; ++c) mine[32 * c + lane] = hidden[c] ? -INFINITY : 0.f;
           __syncwarp();
         }
         if (j + 1 < n) fetch_flags(problem, (j + 1) * kTileRows, flags);
