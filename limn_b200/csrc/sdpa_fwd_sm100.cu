@@ -79,16 +79,11 @@ struct FwdLayout {
   // group's two blocks take turns in. Used at head dim 128 under a causal mask, where it is worth 2 to 3 %: the two
   // Q tiles of an item end at different times there and each group's stores are on its own critical path. Without
   // a causal mask both groups reach the epilogue together and the hand-overs cost more than the stores did (-1 %
-  // at head dim 128, -6 % at 64, measured); with a key mask there is no shared memory left for the block.
-#ifdef LIMN_TILE_STORE_ALL
-  static constexpr bool kTileStore = !(D == 128 && kMask);
-#else
-  static constexpr bool kTileStore = D == 128 && kCausal && !kMask;
-#endif
+  // at head dim 128, -6 % at 64, measured).
+  static constexpr bool kTileStore = D == 128 && kCausal;
   static constexpr int kStageOff = kVOff + kStages * kTileBytes;
   static constexpr int kBarOff = kStageOff + (kTileStore ? kQTiles * kAtomBytes : 0);
-  static constexpr int kBiasOff = kBarOff + 512;            // room for 64 barriers; then, key-mask kernels only: [8 warps][2 buffers][128] floats, 0 or -inf per key
-  static constexpr int kBytes = kBiasOff + (kMask ? 8 * 1024 : 0) + 1024;  // + slack to align the base to 1024
+  static constexpr int kBytes = kBarOff + 512 + 1024;       // room for 64 barriers + slack to align the base to 1024
   // tensor-memory columns
   static constexpr int kSCol = 0;                           // S_t at kSCol + 128 t (P_t overlays its first 64)
   static constexpr int kOCol = 256;                         // O_t at kOCol + D t
@@ -407,9 +402,8 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     unsigned tiles = 0;   // key tiles this group has been through, over all items
     unsigned o_uses = 0;  // items this group has finished
     unsigned stores = 0;  // staging blocks this group has handed to TMA
-    // Key mask: a hidden key is a score of -inf for every row. Each warp keeps its own copy of the tile's 128
-    // flags in shared memory as an additive 0 / -inf, each lane fetching four of them one tile ahead of use.
-    float* bias = reinterpret_cast<float*>(smem_unaligned + (base - raw) + L::kBiasOff) + warp * 256;
+    // Key mask: a hidden key is a score of -inf for every row. Each lane fetches four of a tile's 128 flags one tile
+    // ahead of their use; a ballot per 32 keys then gives every thread all of them.
     // (the flags stay as loaded until the next tile needs them: a warp issues in order, so turning them into anything
     // right after the load would stall it for the load's latency, every tile)
     auto fetch_flags = [&](int problem, int kv0, unsigned (&out4)[4]) {
@@ -435,19 +429,15 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     unsigned flags[4] = {1u, 1u, 1u, 1u};
     if (kMask) fetch_flags(problem, 0, flags);
     for (int j = 0; j < n; ++j, ++tiles) {
-      // a tile none of whose keys is hidden (every tile but the last few of a padded batch) takes no bias at all
+      // Key mask: which of the tile's 128 keys are hidden, as four ballot words in registers (each lane fetched four
+      // of the flags a tile ahead). A tile none of whose keys is hidden (every tile but the last few of a padded
+      // batch) is handled like an unmasked one.
+      unsigned hid[4] = {0u, 0u, 0u, 0u};
       bool any_hidden = false;
       if (kMask) {
-        bool hidden[4];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) hidden[c] = (flags[c] & 0x7fffu) == 0u;
-        any_hidden = __any_sync(0xffffffffu, hidden[0] || hidden[1] || hidden[2] || hidden[3]);
-        if (any_hidden) {
-          float* mine = bias + (j & 1) * 128;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) mine[32 * c + lane] = hidden[c] ? -INFINITY : 0.f;
-          __syncwarp();
-        }
+        for (int c = 0; c < 4; ++c) hid[c] = __ballot_sync(0xffffffffu, (flags[c] & 0x7fffu) == 0u);
+        any_hidden = ((hid[0] | hid[1]) | (hid[2] | hid[3])) != 0u;
         if (j + 1 < n) fetch_flags(problem, (j + 1) * kTileRows, flags);
       }
       ok = __all_sync(0xffffffffu, mbar_wait(bar(B::s_full + t), tiles & 1u, prm.status, 0x0300u | t));  // warp-uniform: the tensor-memory ops below are warp-wide
@@ -462,26 +452,14 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const int kv0 = j * kTileRows;
       const bool diagonal = kCausal && kv0 + kTileRows > item.q0[t];     // some key of this tile is right of some row
       const bool ragged = kv0 + kTileRows > prm.t_k;                // some key of this tile does not exist
-      if (diagonal || ragged) {
+      if (diagonal || ragged || (kMask && any_hidden)) {
         int limit = prm.t_k - kv0;                                  // keys [0, limit) of the tile are visible
         if (kCausal) limit = min(limit, row - kv0 + 1);
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (c * 32 + i >= limit) s[c][i] = 0xff800000u;  // -inf
-      }
-      if (kMask && any_hidden) {
-        const float2* mine = reinterpret_cast<const float2*>(bias + (j & 1) * 128);
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float2 b = mine[(c * 32 + i) >> 1];
-            float lo, hi;
-            f2_unpack(f2_add(f2_pack_bits(s[c][i], s[c][i + 1]), f2_pack(b.x, b.y)), lo, hi);
-            s[c][i] = __float_as_uint(lo), s[c][i + 1] = __float_as_uint(hi);
-          }
+            if (c * 32 + i >= limit || (kMask && ((hid[c] >> i) & 1u) != 0u)) s[c][i] = 0xff800000u;  // -inf
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
